@@ -1,5 +1,5 @@
-from .manager import CacheGroup, CacheManager, LayerCache, PagedKeyValues, PagedNeed, RequestState
+from .manager import CacheGroup, CacheManager, LayerCache, PagedKeyValues, PagedNeed, PagedRows, RequestState
 from .pages import PageCapacityError, PagePool
 
-__all__ = ["CacheGroup", "CacheManager", "LayerCache", "PagedKeyValues", "PagedNeed", "RequestState",
+__all__ = ["CacheGroup", "CacheManager", "LayerCache", "PagedKeyValues", "PagedNeed", "PagedRows", "RequestState",
            "PageCapacityError", "PagePool"]

@@ -52,6 +52,7 @@ class PagedKeyValues(PagedNeed):
     value_dim: Optional[int] = None  # size of a value head where it differs from head_dim
     chunk: Optional[int] = None      # n: positions come in chunks of n from the start of the sequence and a query sees
                                      # its own chunk only, so a page that lies wholly before the newest chunk is done with
+    keep_first: int = 0              # behind a window, the first n keys stay visible: their pages are never given back
 
     def page_shape(self, page_size):
         if self.value_dim is None or self.value_dim == self.head_dim:
@@ -73,17 +74,39 @@ class PagedKeyValues(PagedNeed):
         spans = [n - 1 for n in (self.window, self.chunk) if n is not None]
         return min(spans) if spans else None
 
+    def kept_positions(self) -> int:
+        """Positions from the start of the sequence that stay needed however long it grows."""
+        return self.keep_first if self.window is not None or self.chunk is not None else 0
+
     @property
     def label(self):
         v = "" if self.value_dim in (None, self.head_dim) else f"v{self.value_dim}"
         c = "" if self.chunk is None else f".c{self.chunk}"
-        return f"kv{self.kv_heads}x{self.head_dim}{v}{c}"
+        f = "" if not self.keep_first else f".f{self.keep_first}"
+        return f"kv{self.kv_heads}x{self.head_dim}{v}{c}{f}"
+
+
+@dataclass(frozen=True)
+class PagedRows(PagedNeed):
+    """One row of ``width`` elements per token (a latent that is a token's key and, in part, its value)."""
+    width: int
+    window: Optional[int] = None
+
+    def page_shape(self, page_size):
+        return (page_size * self.width,)
+
+    @property
+    def label(self):
+        return f"rows{self.width}"
 
 
 @dataclass(frozen=True)
 class RequestState:
+    """Fixed-size state of a request at one cache site. A site may have one state without a name (``LayerCache.state``)
+    and any number with names (``LayerCache.named[name]``), e.g. a mixer's and its block arrangement's."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+    name: str = ""
 
 
 class CacheGroup:
@@ -100,6 +123,11 @@ class CacheGroup:
     def name(self):
         w = "all" if self.need.window is None else f"w{self.need.window}"
         return f"{self.need.label}.{w}"
+
+    def kept_blocks(self) -> int:
+        """Blocks from the start of a sequence that are never given back (first keys that stay visible behind a window)."""
+        kept = getattr(self.need, "kept_positions", None)
+        return 0 if kept is None else self.pool.pages_for(kept())
 
     def first_needed_block(self, length: int) -> int:
         """Blocks before this one hold only keys that no later query can see."""
@@ -121,7 +149,7 @@ class CacheGroup:
             (None if self.need.window is None else self.need.window - 1)
         if span is None:
             return full
-        return min(full, self.pool.pages_for(span + max_step_tokens) + 1)
+        return min(full, self.pool.pages_for(span + max_step_tokens) + 1 + self.kept_blocks())
 
 
 class CacheManager:
@@ -138,19 +166,28 @@ class CacheManager:
         self.max_blocks = (max_context + page_size - 1) // page_size
         n_pages = kv_tokens // page_size
         by_need = {}
-        self.state_needs = {}                     # layer -> RequestState
+        self.state_needs = {}                     # layer -> its RequestState without a name
+        self.named_state_needs = {}               # layer -> {name: RequestState}
         for layer, needs in enumerate(layer_needs):
             for need in needs or ():
                 if isinstance(need, PagedNeed):
                     by_need.setdefault(need, []).append(layer)
                 elif isinstance(need, RequestState):
-                    self.state_needs[layer] = need
+                    if need.name:
+                        if need.name in self.named_state_needs.setdefault(layer, {}):
+                            raise ValueError(f"layer {layer}: two states are named {need.name!r}")
+                        self.named_state_needs[layer][need.name] = need
+                    elif layer in self.state_needs:
+                        raise ValueError(f"layer {layer}: two states without a name")
+                    else:
+                        self.state_needs[layer] = need
                 else:
                     raise TypeError(f"layer {layer}: unknown cache need {need!r}")
         self.groups = [CacheGroup(need, layers, n_pages, page_size, max_requests, self.max_blocks)
                        for need, layers in by_need.items()]
         self.group_of_layer = {layer: g for g in self.groups for layer in g.layers}
         self.state = {}                           # layer -> device tensor [max_requests, *shape]
+        self.named_state = {}                     # layer -> {name: device tensor [max_requests, *shape]}
         self._free_slots = list(reversed(range(max_requests)))
         self.slot_of = {}                         # request id -> slot
         self.length = {}                          # request id -> tokens in the cache
@@ -164,9 +201,15 @@ class CacheManager:
         for g in self.groups:
             total += len(g.layers) * g.pool.n_pages * math.prod(g.page_shape) * element_size
         widths = {"float32": 4, "bfloat16": 2, "float16": 2, "int32": 4, "int64": 8, "float64": 8}
-        for need in self.state_needs.values():
+        for need in self._all_state_needs():
             total += self.max_requests * math.prod(need.shape) * widths.get(need.dtype, 4)
         return total
+
+    def _all_state_needs(self):
+        return list(self.state_needs.values()) + [n for named in self.named_state_needs.values() for n in named.values()]
+
+    def _all_states(self):
+        return list(self.state.values()) + [t for named in self.named_state.values() for t in named.values()]
 
     def allocate(self, device, dtype):
         import torch
@@ -175,13 +218,17 @@ class CacheManager:
         for layer, need in self.state_needs.items():
             self.state[layer] = torch.zeros((self.max_requests, *need.shape), device=device,
                                             dtype=getattr(torch, need.dtype))
+        for layer, named in self.named_state_needs.items():
+            self.named_state[layer] = {name: torch.zeros((self.max_requests, *need.shape), device=device,
+                                                         dtype=getattr(torch, need.dtype)) for name, need in named.items()}
 
     def layer_view(self, layer, writable=True):
         """What a mixer sees of the cache: its group's arena slice and its state rows.
         ``layer`` counts the entries of ``layer_needs`` (the stops of the model's run order)."""
         g = self.group_of_layer.get(layer)
         return LayerCache(group=g, kv=None if g is None or g.arena is None else g.arena[g.layers.index(layer)],
-                          state=self.state.get(layer), page_size=self.page_size, writable=writable)
+                          state=self.state.get(layer), page_size=self.page_size, writable=writable,
+                          named=self.named_state.get(layer, {}))
 
     def bytes_per_token(self, element_size):
         import math
@@ -197,7 +244,7 @@ class CacheManager:
         self.slot_of[request], self.length[request] = slot, 0
         for g in self.groups:
             g.tables[request] = []
-        for tensor in self.state.values():
+        for tensor in self._all_states():
             tensor[slot].zero_()
         return slot
 
@@ -260,13 +307,14 @@ class CacheManager:
         self.length[request] = new_length
         for g in self.groups:
             first = g.first_needed_block(new_length)
+            kept = g.kept_blocks()
             table = g.tables[request]
-            gone = [p for p in table[:first] if p >= 0]
+            gone = [p for p in table[kept:first] if p >= 0]
             if gone:
                 g.pool.give_back(request, gone)
-                for i in range(min(first, len(table))):
+                for i in range(kept, min(first, len(table))):
                     table[i] = -1
-                g.table_array[self.slot_of[request], :min(first, len(table))] = -1
+                g.table_array[self.slot_of[request], kept:min(first, len(table))] = -1
 
     def release(self, request):
         """Give back every page and the slot. Safe to call for a request that is not live."""
@@ -312,6 +360,7 @@ class LayerCache:
     state: object
     page_size: int
     writable: bool = True      # False: this mixer reads another stop's cache and must not write it
+    named: dict = None         # states with names, {name: rows [max_requests, ...]} (see RequestState)
 
     @property
     def pages(self):

@@ -16,11 +16,25 @@
 // multiplies a head's output by its logistic function, in float32, before the result is rounded. With n_splits > 1 the
 // key range is cut in n_splits pieces whose (max, sum, unnormalised output) go to
 // scratch and dd_attention_merge combines them.
+//
+// More of the mask and the softmax, all optional (RowsExtra): keep_first = n keeps the first n keys of the sequence
+// visible behind a window (the query then walks keys 0..min(n, lo)-1 and lo..p as one run); softcap = c replaces a
+// scaled score s by c * tanh(s / c); sink, one float32 per head, adds exp(sink) to the softmax's denominator (a key
+// without a value: it is not scaled, not capped and counts once, where the splits are merged); values_in_keys: a
+// page holds key rows only and a value is the first dv elements of its key row (one latent row per token that is
+// both).
 #include "common.cuh"
 #include <math_constants.h>
 
 namespace {
 constexpr int WARPS = 4;
+
+struct RowsExtra {
+    int keep_first;        // 0: none
+    float softcap;         // 0: none
+    const float* sink;     // null: none
+    int values_in_keys;    // 0: a page is a key plane followed by a value plane
+};
 
 template <typename T> struct Vec;
 template <> struct Vec<float> {
@@ -53,7 +67,7 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                       T* __restrict__ out, int out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int n_tokens, int H, int KH, int d, int P, int n_pages, int window, float scale,
                       int n_splits, int* __restrict__ error_flag, int dv, int chunk,
-                      const T* __restrict__ gate, int gate_stride) {
+                      const T* __restrict__ gate, int gate_stride, RowsExtra extra) {
     extern __shared__ float q_smem[];
     dd_launch_dependents();
     dd_grid_wait();
@@ -67,10 +81,14 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     const int kh = h / (H / KH);
     int lo = window > 0 ? max(0, pos - window + 1) : 0;
     if (chunk > 0) lo = max(lo, pos - pos % chunk);
-    const int hi = pos + 1;
-    int per = (hi - lo + n_splits - 1) / n_splits;
+    // the keys a query walks are numbered as one run: the kept first keys (those the window no longer covers), then
+    // the window; run index i is key i below n_first, else key i + skip
+    const int n_first = (window > 0 || chunk > 0) ? min(extra.keep_first, lo) : 0;
+    const int skip = lo - n_first;
+    const int hi = pos + 1 - skip;
+    int per = (hi + n_splits - 1) / n_splits;
     per = (per + 31) / 32 * 32;
-    const int k0 = lo + split * per;
+    const int k0 = split * per;
     const int k1 = min(hi, k0 + per);
 
     float* qs = q_smem + warp * d;
@@ -79,16 +97,19 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     __syncwarp();
 
     const int* bt = block_table + (size_t)tok_entry[t] * max_blocks;
-    const size_t key_plane = (size_t)P * d, value_plane = (size_t)P * dv;
+    const size_t key_plane = (size_t)P * d, value_plane = extra.values_in_keys ? 0 : (size_t)P * dv;
     const size_t page_elems = (size_t)KH * (key_plane + value_plane);
+    const size_t value_row = extra.values_in_keys ? (size_t)d : (size_t)dv;      // elements between two value rows
+    const size_t value_base = extra.values_in_keys ? (size_t)kh * key_plane : (size_t)KH * key_plane + (size_t)kh * value_plane;
     const bool wide = d % Vec<T>::N == 0 && page_elems % Vec<T>::N == 0;   // key rows are whole, aligned 16-byte pieces
     float m = -CUDART_INF_F, l = 0.f, o[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) o[i] = 0.f;
 
     for (int base = k0; base < k1; base += 32) {
-        const int key = base + lane;
-        bool valid = key < k1;
+        const int run = base + lane;
+        bool valid = run < k1;
+        const int key = run < n_first ? run : run + skip;
         int page = 0;
         if (valid) {
             const int blk = key / P;
@@ -114,7 +135,7 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
             } else {
                 for (int c = 0; c < d; ++c) acc = fmaf(qs[c], dd_to_f32(kp[c]), acc);
             }
-            sc = acc;
+            sc = extra.softcap > 0.f ? extra.softcap * tanhf(acc / extra.softcap) : acc;
         }
         const float cm = dd_warp_max(sc);
         if (cm == -CUDART_INF_F) continue;
@@ -135,8 +156,8 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                 const int j = min(j0 + u, n_valid - 1);     // past the last key: its row again, never added
                 pj[u] = __shfl_sync(0xffffffffu, p, j);
                 const int pg = __shfl_sync(0xffffffffu, page, j);
-                const T* vp = cache + (size_t)pg * page_elems + (size_t)KH * key_plane + (size_t)kh * value_plane +
-                              (size_t)((base + j) % P) * dv;
+                const int kj = __shfl_sync(0xffffffffu, key, j);
+                const T* vp = cache + (size_t)pg * page_elems + value_base + (size_t)(kj % P) * value_row;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
                     const int c = lane + 32 * i;
@@ -152,6 +173,15 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
         }
     }
     if (n_splits == 1) {
+        if (extra.sink) {
+            // the sink joins the sum as one more term exp(sink - maximum), the maximum taken over it too
+            const float sk = extra.sink[h];
+            const float m_all = fmaxf(m, sk);
+            const float corr = m == -CUDART_INF_F ? 0.f : expf(m - m_all);
+            l = l * corr + expf(sk - m_all);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[i] *= corr;
+        }
         float inv = l > 0.f ? 1.0f / l : 0.f;
         if (gate) inv *= 1.0f / (1.0f + expf(-dd_to_f32(gate[(size_t)t * gate_stride + h])));
         T* op = out + (size_t)t * out_stride + (size_t)h * dv;
@@ -178,7 +208,7 @@ template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                        T* __restrict__ out, int out_stride, int n_tokens, int H, int d, int n_splits,
-                       const T* __restrict__ gate, int gate_stride) {
+                       const T* __restrict__ gate, int gate_stride, const float* __restrict__ sink) {
     dd_launch_dependents();
     dd_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -194,10 +224,10 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
         // order as the plain loops below, without a trip to memory for every term (14 -> 3 us for 200 rows x 9 splits).
         const float my_m = lane < n_splits ? ml[2 * lane] : -CUDART_INF_F;
         const float my_l = lane < n_splits ? ml[2 * lane + 1] : 0.f;
-        float m = -CUDART_INF_F;
+        float m = sink ? sink[h] : -CUDART_INF_F;
         for (int s = 0; s < n_splits; ++s) m = fmaxf(m, __shfl_sync(0xffffffffu, my_m, s));
         const float my_w = my_l > 0.f ? expf(my_m - m) : 0.f;
-        float l = 0.f;
+        float l = sink ? expf(sink[h] - m) : 0.f;
         for (int s = 0; s < n_splits; ++s) {
             const float ls = __shfl_sync(0xffffffffu, my_l, s), ws = __shfl_sync(0xffffffffu, my_w, s);
             if (ls > 0.f) l += ls * ws;
@@ -222,9 +252,9 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
         }
         return;
     }
-    float m = -CUDART_INF_F;
+    float m = sink ? sink[h] : -CUDART_INF_F;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
-    float l = 0.f;
+    float l = sink ? expf(sink[h] - m) : 0.f;
     for (int s = 0; s < n_splits; ++s)
         if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
     const float inv = (l > 0.f ? 1.0f / l : 0.f) * gated;
@@ -240,7 +270,7 @@ template <typename T>
 int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_entry, const int* tok_pos,
                 const int* block_table, int max_blocks, void* out, int out_stride, float* part_o, float* part_ml,
                 int n_tokens, int H, int KH, int d, int P, int n_pages, int window, float scale, int n_splits,
-                int* error_flag, cudaStream_t s, int dv, int chunk, const void* gate, int gate_stride) {
+                int* error_flag, cudaStream_t s, int dv, int chunk, const void* gate, int gate_stride, RowsExtra extra) {
     const long long items = (long long)n_tokens * H * n_splits;
     if ((items + WARPS - 1) / WARPS > 0x7fffffffLL)
         return dd_fail("dd_attention_rows: %d tokens x %d heads x %d splits are more work items than one launch takes",
@@ -250,7 +280,7 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
 #define DD_ROWS(DPL)                                                                                        \
     dd_launch(attention_rows_kernel<T, DPL>, dim3(grid), dim3(WARPS * 32), smem, s, (const T*)q, q_stride, (const T*)cache,    \
         tok_entry, tok_pos, block_table, max_blocks, (T*)out, out_stride, part_o, part_ml, n_tokens, H, KH, \
-        d, P, n_pages, window, scale, n_splits, error_flag, dv, chunk, (const T*)gate, gate_stride)
+        d, P, n_pages, window, scale, n_splits, error_flag, dv, chunk, (const T*)gate, gate_stride, extra)
     if (dv <= 32) DD_ROWS(1);
     else if (dv <= 64) DD_ROWS(2);
     else if (dv <= 128) DD_ROWS(4);
@@ -259,7 +289,7 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
     if (int e = dd_check_launch("dd_attention_rows")) return e;
     if (n_splits > 1) {
         dd_launch(attention_merge_kernel<T>, dim3(dd_ceil_div((long long)n_tokens * H, WARPS)), dim3(WARPS * 32), 0, s, 
-            part_o, part_ml, (T*)out, out_stride, n_tokens, H, dv, n_splits, (const T*)gate, gate_stride);
+            part_o, part_ml, (T*)out, out_stride, n_tokens, H, dv, n_splits, (const T*)gate, gate_stride, extra.sink);
         return dd_check_launch("dd_attention_merge");
     }
     return 0;
@@ -274,13 +304,19 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
 // dd_attention_rows_masked takes four more: v_dim, the size of a value head (head_dim where keys and values have one
 // size; out then has heads of v_dim and the scratch v_dim floats per item); chunk, the chunk size of the mask (0: none);
 // gate and gate_stride, row views like q with one element per head (null: no gate).
-DD_API int dd_attention_rows_masked(const void* q, int q_stride, const void* cache, const int* tok_entry,
+//
+// dd_attention_rows_sinks takes four more again: keep_first (0: none), softcap (0: none), sink (float32 [n_heads] or null)
+// and values_in_keys (see the head of this file).
+DD_API int dd_attention_rows_sinks(const void* q, int q_stride, const void* cache, const int* tok_entry,
                              const int* tok_pos, const int* block_table, int max_blocks, void* out, int out_stride,
                              float* part_o, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
                              int head_dim, int page_size, int n_pages, int window, float scale, int n_splits,
                              int dtype, int* error_flag, void* stream, int v_dim, int chunk, const void* gate,
-                             int gate_stride) {
+                             int gate_stride, int keep_first, float softcap, const float* sink, int values_in_keys) {
     if (n_tokens <= 0) return 0;
+    if (keep_first < 0 || softcap < 0.f) return dd_fail("dd_attention_rows: keep_first %d and softcap %g must not be negative", keep_first, softcap);
+    if (values_in_keys && v_dim > head_dim) return dd_fail("dd_attention_rows: a value of %d elements does not lie in a key row of %d", v_dim, head_dim);
+    const RowsExtra extra = {keep_first, softcap, sink, values_in_keys ? 1 : 0};
     if (head_dim <= 0 || head_dim > 256 || v_dim <= 0 || v_dim > 256)
         return dd_fail("dd_attention_rows: head sizes %d and %d are not supported (at most 256)", head_dim, v_dim);
     if (window < 0 || chunk < 0) return dd_fail("dd_attention_rows: window %d and chunk %d must not be negative", window, chunk);
@@ -292,13 +328,24 @@ DD_API int dd_attention_rows_masked(const void* q, int q_stride, const void* cac
     if (dtype == DD_F32)
         return launch_rows<float>(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out, out_stride,
                                   part_o, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, page_size, n_pages,
-                                  window, scale, n_splits, error_flag, s, v_dim, chunk, gate, gate_stride);
+                                  window, scale, n_splits, error_flag, s, v_dim, chunk, gate, gate_stride, extra);
     if (dtype == DD_BF16)
         return launch_rows<__nv_bfloat16>(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out,
                                           out_stride, part_o, part_ml, n_tokens, n_heads, n_kv_heads, head_dim,
                                           page_size, n_pages, window, scale, n_splits, error_flag, s, v_dim, chunk, gate,
-                                          gate_stride);
+                                          gate_stride, extra);
     return dd_fail("dd_attention_rows: unknown dtype %d", dtype);
+}
+
+DD_API int dd_attention_rows_masked(const void* q, int q_stride, const void* cache, const int* tok_entry,
+                             const int* tok_pos, const int* block_table, int max_blocks, void* out, int out_stride,
+                             float* part_o, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
+                             int head_dim, int page_size, int n_pages, int window, float scale, int n_splits,
+                             int dtype, int* error_flag, void* stream, int v_dim, int chunk, const void* gate,
+                             int gate_stride) {
+    return dd_attention_rows_sinks(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out, out_stride, part_o,
+                                   part_ml, n_tokens, n_heads, n_kv_heads, head_dim, page_size, n_pages, window, scale,
+                                   n_splits, dtype, error_flag, stream, v_dim, chunk, gate, gate_stride, 0, 0.f, nullptr, 0);
 }
 
 DD_API int dd_attention_rows(const void* q, int q_stride, const void* cache, const int* tok_entry,

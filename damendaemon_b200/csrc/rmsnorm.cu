@@ -2,6 +2,14 @@
 // the sum of squares and the scaling in float32. `offset` is 0 for a weight stored as the factor itself and 1 for a
 // weight stored as its distance from one. Output in the engine dtype. An optional row index gathers rows first (the
 // final norm runs only where logits are wanted).
+//
+// In groups: the row is cut into `groups` equal consecutive stretches and each is divided by its own root mean square;
+// the weight multiplies the whole row. With a shift (dd_rmsnorm_shift) the normed row n[t] is blended, in float32 and
+// per channel, with the normed row of the token before it in its sequence: out[t] = n[t] + (n[t-1] - n[t]) * mu.
+// n[t-1] of a step's first token is the float32 row the request's state slot holds (zeros for a new request); the
+// block of that first token also leaves the normed row of the entry's last token there, after it has read the old one,
+// so one block alone touches a slot's row. A block norms its own row and the row before it with the same function, so
+// n[t-1] has the same bits whether it comes from the state or is computed again.
 #include "common.cuh"
 
 namespace {
@@ -84,7 +92,114 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index, c
     const float r = 1.0f / sqrtf(rms_block_sum<THREADS>(sq, scratch) / (float)width + eps);
     for (int c = threadIdx.x; c < width; c += THREADS) o[c] = dd_from_f32<TO>(in[c] * r * (offset + weight[c]));
 }
+constexpr int MAX_GROUPS = 64;
+
+// The inverse root mean squares of a row's stretches into r[0 .. groups) (shared memory); every thread sees them after.
+template <int THREADS>
+__device__ __forceinline__ void group_scales(const float* __restrict__ in, int width, int groups, float eps, float* r,
+                                             float* scratch) {
+    const int gw = width / groups;
+    for (int g = 0; g < groups; ++g) {
+        const float* part = in + (size_t)g * gw;
+        float sq = 0.f;
+        for (int c = threadIdx.x; c < gw; c += THREADS) sq = fmaf(part[c], part[c], sq);
+        const float total = rms_block_sum<THREADS>(sq, scratch);
+        if (threadIdx.x == 0) r[g] = 1.0f / sqrtf(total / (float)gw + eps);
+    }
+    __syncthreads();
+}
+
+template <typename TO, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_groups_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ weight,
+                      TO* __restrict__ out, int width, int groups, float eps, float offset) {
+    __shared__ float scratch[THREADS / 32];
+    __shared__ float r[MAX_GROUPS];
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int row = blockIdx.x;
+    const float* in = x + (size_t)(row_index ? row_index[row] : row) * width;
+    TO* o = out + (size_t)row * width;
+    group_scales<THREADS>(in, width, groups, eps, r, scratch);
+    const int gw = width / groups;
+    for (int c = threadIdx.x; c < width; c += THREADS) o[c] = dd_from_f32<TO>(in[c] * r[c / gw] * (offset + weight[c]));
+}
+
+template <typename TO, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ mu,
+                     float* __restrict__ state, const int* __restrict__ tok_entry, const int* __restrict__ entry_start,
+                     const int* __restrict__ entry_slot, TO* __restrict__ out, int width, int groups, float eps, float offset) {
+    __shared__ float scratch[THREADS / 32];
+    __shared__ float r_own[MAX_GROUPS], r_other[MAX_GROUPS];
+    dd_launch_dependents();
+    const int t = blockIdx.x;
+    const int e = tok_entry[t];
+    const int first = entry_start[e], last = entry_start[e + 1] - 1;
+    float* kept = state + (size_t)entry_slot[e] * width;
+    dd_grid_wait();
+    const float* in = x + (size_t)t * width;
+    const int gw = width / groups;
+    TO* o = out + (size_t)t * width;
+    group_scales<THREADS>(in, width, groups, eps, r_own, scratch);
+    if (t != first) {
+        // the token before lies in this step: its normed row again, by the same arithmetic
+        const float* before = in - width;
+        group_scales<THREADS>(before, width, groups, eps, r_other, scratch);
+        for (int c = threadIdx.x; c < width; c += THREADS) {
+            const float w = offset + weight[c];
+            const float n = in[c] * r_own[c / gw] * w, p = before[c] * r_other[c / gw] * w;
+            o[c] = dd_from_f32<TO>(n + (p - n) * mu[c]);
+        }
+        return;
+    }
+    // the first token of its entry in this step: the row before it is the state's; then the state becomes the entry's
+    // last normed row (a thread writes only the channels it has read)
+    const float* tail = x + (size_t)last * width;
+    if (last != t) group_scales<THREADS>(tail, width, groups, eps, r_other, scratch);
+    for (int c = threadIdx.x; c < width; c += THREADS) {
+        const float w = offset + weight[c];
+        const float n = in[c] * r_own[c / gw] * w, p = kept[c];
+        o[c] = dd_from_f32<TO>(n + (p - n) * mu[c]);
+        kept[c] = last != t ? tail[c] * r_other[c / gw] * w : n;
+    }
+}
 }  // namespace
+
+// The norm in groups and the blend with the token before (see the head of this file). state: float32 [slots, width].
+DD_API int dd_rmsnorm_shift(const float* x, const float* weight, const float* mu, float* state, const int* tok_entry,
+                            const int* entry_start, const int* entry_slot, void* out, int rows, int width, int groups,
+                            float eps, float offset, int out_dtype, void* stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || groups <= 0 || groups > MAX_GROUPS || width % groups)
+        return dd_fail("dd_rmsnorm_shift: a row of %d does not fall into %d equal stretches (at most %d)", width, groups, MAX_GROUPS);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == DD_F32)
+        dd_launch(rmsnorm_shift_kernel<float, 256>, dim3(rows), dim3(256), 0, s, x, weight, mu, state, tok_entry, entry_start,
+                  entry_slot, (float*)out, width, groups, eps, offset);
+    else if (out_dtype == DD_BF16)
+        dd_launch(rmsnorm_shift_kernel<__nv_bfloat16, 256>, dim3(rows), dim3(256), 0, s, x, weight, mu, state, tok_entry,
+                  entry_start, entry_slot, (__nv_bfloat16*)out, width, groups, eps, offset);
+    else
+        return dd_fail("dd_rmsnorm_shift: unknown output dtype %d", out_dtype);
+    return dd_check_launch("dd_rmsnorm_shift");
+}
+
+DD_API int dd_rmsnorm_groups(const float* x, const int* row_index, const float* weight, void* out, int rows, int width,
+                             int groups, float eps, float offset, int out_dtype, void* stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || groups <= 0 || groups > MAX_GROUPS || width % groups)
+        return dd_fail("dd_rmsnorm_groups: a row of %d does not fall into %d equal stretches (at most %d)", width, groups, MAX_GROUPS);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == DD_F32)
+        dd_launch(rmsnorm_groups_kernel<float, 256>, dim3(rows), dim3(256), 0, s, x, row_index, weight, (float*)out, width, groups, eps, offset);
+    else if (out_dtype == DD_BF16)
+        dd_launch(rmsnorm_groups_kernel<__nv_bfloat16, 256>, dim3(rows), dim3(256), 0, s, x, row_index, weight,
+                  (__nv_bfloat16*)out, width, groups, eps, offset);
+    else
+        return dd_fail("dd_rmsnorm_groups: unknown output dtype %d", out_dtype);
+    return dd_check_launch("dd_rmsnorm_groups");
+}
 
 DD_API int dd_rmsnorm(const float* x, const int* row_index, const float* weight, void* out, int rows, int width,
                       float eps, float offset, int out_dtype, void* stream) {

@@ -65,6 +65,8 @@ class Engine:
             from ..registry import architecture_of
             self.architecture = architecture_of(config)
             self.config = self.architecture.parse_config(config)
+            if self.architecture.sizes_from_shapes is not None:
+                self.config = self.architecture.sizes_from_shapes(self.config, {n: tuple(t.shape) for n, t in tensors.items()})
         self.spec = self.architecture.build_spec(self.config)
         decls = tensor_decls(self.spec)
         if model_dir is not None:
@@ -94,6 +96,9 @@ class Engine:
         self.cache.allocate(self.device, self.dtype)
         self._caches = [self.cache.layer_view(i) if e.cache_of is None else self.cache.layer_view(e.cache_of, writable=False)
                         for i, e in enumerate(self.spec.run_order)]
+        for i, e in enumerate(self.spec.run_order):
+            if e.cache_of is not None:           # another stop's pages, but the named states of its own site
+                self._caches[i].named = self.cache.named_state.get(i, {})
         self.check_device_errors = check_device_errors
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_graph = use_graph and self.model.graph_safe

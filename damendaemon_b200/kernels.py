@@ -31,6 +31,18 @@ _SIGNATURES = {
         "dd_embed": [_c_void] * 5 + [_c_int] * 5 + [_c_float, _c_void, _c_void],
         "dd_layernorm": [_c_void] * 5 + [_c_int, _c_int, _c_float, _c_int, _c_void],
         "dd_rmsnorm": [_c_void] * 4 + [_c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+        "dd_rmsnorm_groups": [_c_void] * 4 + [_c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+        "dd_rmsnorm_shift": [_c_void] * 8 + [_c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+        "dd_weighted_sum": [_c_void, ctypes.c_longlong, _c_void, _c_int, _c_void, _c_void],
+        "dd_blend_rows": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void],
+        "dd_delta_state_rows": [_c_int],
+        "dd_delta_prepare": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int] + [_c_void] * 11 + [_c_int] * 6 + [_c_void],
+        "dd_conv_state_update": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
+        "dd_delta_rule": [_c_void] * 7 + [_c_int, _c_void, _c_void] + [_c_int] * 4 + [_c_void],
+        "dd_delta_finish": [_c_void] * 4 + [_c_int] * 4 + [_c_float, _c_int, _c_void],
+        "dd_latent_prepare": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_int, _c_void, _c_float, _c_void, _c_int,
+                              _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
+        "dd_per_head_linear": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int] + [_c_int] * 6 + [_c_void],
         "dd_rotary": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_float] + [_c_int] * 7 + [_c_void],
         "dd_gemm_simt_group_tile": [],
         "dd_gemm_simt_grouped": [_c_void, _c_int, _c_void, _c_int, ctypes.c_longlong, _c_void, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
@@ -49,6 +61,9 @@ _SIGNATURES = {
                              + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void],
         "dd_attention_rows_masked": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
                                     + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int],
+        "dd_attention_rows_sinks": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
+                                   + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int,
+                                      _c_int, _c_float, _c_void, _c_int],
         "dd_sample": [_c_void, _c_int, _c_int, _c_int] + [_c_void] * 6,
         "dd_adjust_logits": [_c_void, _c_int, _c_int] + [_c_void] * 8 + [_c_int, _c_void],
     },
@@ -266,8 +281,9 @@ def layernorm(x, gamma, beta, eps, out_dtype, row_index=None, out=None):
     return out
 
 
-def rmsnorm(x, weight, eps, out_dtype, row_index=None, offset=0.0, out=None):
-    """x / sqrt(mean(x^2) + eps) * (offset + weight) over float32 rows; offset 1 for a weight stored around zero."""
+def rmsnorm(x, weight, eps, out_dtype, row_index=None, offset=0.0, out=None, groups=1):
+    """x / sqrt(mean(x^2) + eps) * (offset + weight) over float32 rows; offset 1 for a weight stored around zero.
+    groups > 1: the row in that many equal consecutive stretches, each divided by its own root mean square."""
     _rows(x, "x")
     rows = x.shape[0] if row_index is None else row_index.numel()
     width = x.shape[1]
@@ -275,9 +291,176 @@ def rmsnorm(x, weight, eps, out_dtype, row_index=None, offset=0.0, out=None):
         raise KernelError("rmsnorm input must be contiguous")
     if out is None:
         out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    if groups != 1:
+        _call(library("core"), "dd_rmsnorm_groups", _ptr(x, "x", torch.float32), _ptr(row_index, "row_index", torch.int32),
+              _ptr(weight, "weight", torch.float32), _ptr(out, "out", out_dtype), rows, width, int(groups), float(eps),
+              float(offset), _dt(out_dtype), _stream())
+        return out
     _call(library("core"), "dd_rmsnorm", _ptr(x, "x", torch.float32), _ptr(row_index, "row_index", torch.int32),
           _ptr(weight, "weight", torch.float32), _ptr(out, "out", out_dtype), rows, width, float(eps), float(offset),
           _dt(out_dtype), _stream())
+    return out
+
+
+def rmsnorm_shift(x, weight, eps, out_dtype, shift, state, token_entry, entry_start, entry_slot, offset=0.0, groups=1, out=None):
+    """The RMS norm (in ``groups`` stretches) of float32 rows, each blended with the normed row of the token before it in its
+    sequence: out[t] = n[t] + (n[t-1] - n[t]) * shift, float32 inside. ``state`` float32 [slots, width] holds the normed row
+    of every request's last token (zeros for a new request): read for an entry's first token, then replaced by the entry's
+    last normed row."""
+    _rows(x, "x")
+    rows, width = x.shape
+    if not x.is_contiguous() or state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1:] != (width,):
+        raise KernelError("rmsnorm_shift: contiguous float32 rows and a float32 state [slots, width] wanted")
+    for v, name in ((weight, "weight"), (shift, "shift")):
+        if v.numel() != width or v.dtype != torch.float32 or not v.is_contiguous():
+            raise KernelError(f"rmsnorm_shift: {name} must be float32 [width]")
+    if out is None:
+        out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    _call(library("core"), "dd_rmsnorm_shift", _ptr(x, "x", torch.float32), _ptr(weight), _ptr(shift), _ptr(state),
+          _ptr(token_entry, "token_entry", torch.int32), _ptr(entry_start, "entry_start", torch.int32),
+          _ptr(entry_slot, "entry_slot", torch.int32), _ptr(out, "out", out_dtype), rows, width, int(groups), float(eps),
+          float(offset), _dt(out_dtype), _stream())
+    return out
+
+
+def weighted_sum(stack, weights, n, out):
+    """out = sum over j < n of weights[j] * stack[j], float32, j ascending. stack: float32 [planes, ...] contiguous;
+    weights: float32 [>= n] on the device; out: float32 of a plane's shape (it may be a later plane of the stack)."""
+    if stack.dtype != torch.float32 or out.dtype != torch.float32 or not stack.is_contiguous() or not out.is_contiguous() or \
+            weights.dtype != torch.float32 or weights.numel() < n or n > stack.shape[0] or out.numel() != stack[0].numel():
+        raise KernelError("weighted_sum: float32 contiguous planes and at least n weights wanted")
+    _call(library("core"), "dd_weighted_sum", _ptr(stack, "stack"), out.numel(), _ptr(weights, "weights"), int(n), _ptr(out, "out"),
+          _stream())
+    return out
+
+
+def blend_rows(v, other, weight):
+    """In place: v <- (1 - weight) * v + weight * other, float32 inside. v, other: row views [N, width] of one element type;
+    weight: one float32 on the device."""
+    if v.shape != other.shape or v.dtype != other.dtype or v.stride(1) != 1 or other.stride(1) != 1 or \
+            weight.dtype != torch.float32 or weight.numel() != 1:
+        raise KernelError("blend_rows: two row views of one shape and type and one float32 weight wanted")
+    _call(library("core"), "dd_blend_rows", _ptr(v, "v"), v.stride(0), _ptr(other, "other"), other.stride(0), _ptr(weight, "weight"),
+          v.shape[0], v.shape[1], _dt(v.dtype), _stream())
+    return v
+
+
+def delta_state_shape(heads, head_dim, value_dim):
+    """Shape of one request's delta-rule state (float32): per head the columns of S one after the other, each padded to the
+    rows the kernel's lanes hold (eight a lane, a power of two of lanes); zeros for a new request."""
+    rows = 0
+    if 0 < head_dim <= 256:
+        lanes = 1
+        while lanes * 8 < head_dim:
+            lanes *= 2
+        rows = 8 * lanes          # what dd_delta_state_rows answers
+    if not rows or value_dim <= 0:
+        raise KernelError(f"delta rule: heads of {head_dim} by {value_dim} are not supported (keys of at most 256)")
+    return (int(heads), int(value_dim), rows)
+
+
+def delta_prepare(proj, beta_in, step_in, conv_w, conv_state, a_log, dt_bias, token_entry, entry_start, entry_slot, heads,
+                  kv_heads, head_dim, value_dim):
+    """The delta rule's operands of a step, float32: (q, k [N, kv_heads*head_dim], v [N, heads*value_dim], decay
+    [N, heads*head_dim], beta [N, heads]). proj: rows whose first elements are the q, k and v projections (a row view);
+    beta_in: a [N, heads] view of the same type; step_in: float32 [N, heads*head_dim] (the decay's low-rank projection);
+    conv_w: float32 [channels, taps]; conv_state: float32 [slots, taps - 1, channels] (read only here). q, k and v pass the
+    causal convolution and silu; q and k become unit vectors per head, q times head_dim^-1/2; beta = sigmoid(beta_in);
+    decay = exp(-exp(a_log[head]) * softplus(step_in + dt_bias))."""
+    n = proj.shape[0]
+    qk, vw = kv_heads * head_dim, heads * value_dim
+    channels, taps = conv_w.shape
+    if channels != 2 * qk + vw or proj.shape[1] < channels or proj.stride(1) != 1 or beta_in.shape != (n, heads) or \
+            beta_in.dtype != proj.dtype or beta_in.stride(1) != 1 or step_in.dtype != torch.float32 or not step_in.is_contiguous() or \
+            step_in.shape != (n, heads * head_dim) or conv_w.dtype != torch.float32 or not conv_w.is_contiguous() or \
+            conv_state.dtype != torch.float32 or not conv_state.is_contiguous() or tuple(conv_state.shape[1:]) != (taps - 1, channels) or \
+            a_log.numel() != heads or dt_bias.numel() != heads * head_dim:
+        raise KernelError("delta_prepare: shapes do not fit the heads")
+    dev = proj.device
+    f32 = lambda w: torch.empty((n, w), dtype=torch.float32, device=dev)
+    q, k, v, decay, beta = f32(qk), f32(qk), f32(vw), f32(heads * head_dim), f32(heads)
+    _call(library("core"), "dd_delta_prepare", _ptr(proj, "proj"), proj.stride(0), _ptr(beta_in, "beta_in"), beta_in.stride(0),
+          _ptr(step_in), _ptr(conv_w), int(taps), _ptr(conv_state), _ptr(a_log, "a_log", torch.float32),
+          _ptr(dt_bias, "dt_bias", torch.float32), _ptr(token_entry, "token_entry", torch.int32),
+          _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_slot, "entry_slot", torch.int32), _ptr(q), _ptr(k), _ptr(v),
+          _ptr(decay), _ptr(beta), n, heads, kv_heads, head_dim, value_dim, _dt(proj.dtype), _stream())
+    return q, k, v, decay, beta
+
+
+def conv_state_update(proj, conv_state, entry_start, entry_slot):
+    """Leave in conv_state [slots, taps - 1, channels] (float32) the last taps - 1 input rows of every entry: what the
+    state held, followed by the step's rows of proj (a row view whose first ``channels`` elements are the inputs)."""
+    keep, channels = conv_state.shape[1], conv_state.shape[2]
+    if proj.shape[1] < channels or proj.stride(1) != 1 or conv_state.dtype != torch.float32 or not conv_state.is_contiguous():
+        raise KernelError("conv_state_update: shapes do not fit")
+    _call(library("core"), "dd_conv_state_update", _ptr(proj, "proj"), proj.stride(0), _ptr(conv_state), keep + 1,
+          _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_slot, "entry_slot", torch.int32), entry_slot.numel(), channels,
+          _dt(proj.dtype), _stream())
+
+
+def delta_rule(q, k, v, decay, beta, entry_start, entry_slot, state, heads, kv_heads, head_dim, value_dim, out=None):
+    """The gated delta rule of a step: per entry and head, from the state in row entry_slot[e] of ``state`` (float32
+    [slots, *delta_state_shape(...)], read and written), token by token: S = decay[:, None] * S; u = beta * (v - S^T k);
+    S = S + k u^T; o = S^T q. Operands float32 as ``delta_prepare`` leaves them. Returns o float32 [N, heads*value_dim]."""
+    n = q.shape[0]
+    ok = all(t.dtype == torch.float32 and t.is_contiguous() for t in (q, k, v, decay, beta, state))
+    if not ok or q.shape != (n, kv_heads * head_dim) or k.shape != q.shape or v.shape != (n, heads * value_dim) or \
+            decay.shape != (n, heads * head_dim) or beta.shape != (n, heads) or \
+            tuple(state.shape[1:]) != delta_state_shape(heads, head_dim, value_dim):
+        raise KernelError("delta_rule: shapes do not fit the state")
+    if out is None:
+        out = torch.empty((n, heads * value_dim), dtype=torch.float32, device=q.device)
+    _call(library("core"), "dd_delta_rule", _ptr(q), _ptr(k), _ptr(v), _ptr(decay), _ptr(beta),
+          _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_slot, "entry_slot", torch.int32), entry_slot.numel(),
+          _ptr(state), _ptr(out), heads, kv_heads, head_dim, value_dim, _stream())
+    return out
+
+
+def delta_finish(o, gate, weight, heads, eps, out_dtype, out=None):
+    """out[t, head] = o[t, head] / sqrt(mean(o[t, head]^2) + eps) * weight * sigmoid(gate[t, head]); o, gate float32
+    [N, heads*dv] contiguous, weight float32 [dv]."""
+    n, total = o.shape
+    if gate.shape != o.shape or gate.dtype != torch.float32 or o.dtype != torch.float32 or not o.is_contiguous() or \
+            not gate.is_contiguous() or total % heads or weight.numel() != total // heads or weight.dtype != torch.float32:
+        raise KernelError("delta_finish: the gate or the weight does not fit the read-out")
+    if out is None:
+        out = torch.empty((n, total), dtype=out_dtype, device=o.device)
+    _call(library("core"), "dd_delta_finish", _ptr(o), _ptr(gate), _ptr(weight), _ptr(out, "out", out_dtype), out.stride(0), n,
+          heads, total // heads, float(eps), _dt(out_dtype), _stream())
+    return out
+
+
+def latent_prepare(q, down, weight, eps, freqs, token_entry, positions, block_table, cache, heads, head_dim, rot_dim, rank):
+    """A step's latent rows into the cache, and its queries rotated. down: [N, rank + rot_dim] row view; the cache row of a
+    token becomes [rms(down[:rank]) * weight | down[rank:] rotated by its position] (cache [pages, page_size * (rank +
+    rot_dim)]); the last rot_dim elements of every query head (q [N, heads * (head_dim + rot_dim)], a row view) are rotated
+    in place. Neighbouring dimensions pair; the first 2 * len(freqs) of the rot_dim turn. float32 inside."""
+    n = q.shape[0]
+    row = rank + rot_dim
+    if q.shape[1] != heads * (head_dim + rot_dim) or q.stride(1) != 1 or down.shape != (n, row) or down.stride(1) != 1 or \
+            q.dtype != down.dtype or cache.dtype != q.dtype or cache.dim() != 2 or cache.shape[1] % row or not cache.is_contiguous() or \
+            weight.numel() != rank or weight.dtype != torch.float32 or freqs.dtype != torch.float32 or 2 * freqs.numel() > rot_dim:
+        raise KernelError("latent_prepare: shapes do not fit")
+    _call(library("core"), "dd_latent_prepare", _ptr(q, "q"), q.stride(0), heads, head_dim, rot_dim, _ptr(down, "down"),
+          down.stride(0), rank, _ptr(weight), float(eps), _ptr(freqs), freqs.numel(), _ptr(token_entry, "token_entry", torch.int32),
+          _ptr(positions, "positions", torch.int32), _ptr(block_table, "block_table", torch.int32), block_table.shape[1],
+          _ptr(cache), cache.shape[0], cache.shape[1] // row, n, _dt(q.dtype), _ptr(error_flag(q.device)), _stream())
+
+
+def per_head_linear(x, w, in_head, out_head=None, tail=0, out=None):
+    """out[t, h, :J] = w[h] @ x[t, h, :I], out[t, h, J:J+tail] = x[t, h, I:I+tail]: every head's piece of a row times the
+    head's own matrix. x: a row view whose head h starts at h * in_head; w: [heads, J, I] contiguous, x's type; out: rows
+    whose head h starts at h * out_head (default J + tail, packed). float32 sums in an order that does not depend on the
+    batch."""
+    heads, J, I = w.shape
+    out_head = J + tail if out_head is None else out_head
+    n = x.shape[0]
+    if x.stride(1) != 1 or w.dtype != x.dtype or not w.is_contiguous() or x.shape[1] < (heads - 1) * in_head + I + tail:
+        raise KernelError("per_head_linear: shapes do not fit")
+    if out is None:
+        out = torch.empty((n, heads * out_head), dtype=x.dtype, device=x.device)
+    _call(library("core"), "dd_per_head_linear", _ptr(x, "x"), x.stride(0), int(in_head), _ptr(w, "w"), _ptr(out, "out"),
+          out.stride(0), int(out_head), n, heads, I, J, int(tail), _dt(x.dtype), _stream())
     return out
 
 
@@ -412,13 +595,25 @@ def kv_store(k, v, token_entry, positions, block_table, cache, n_tokens=None, kv
 
 
 def attention_rows(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None,
-                   chunk=None, gate=None, kv_heads=None, v_dim=None):
+                   chunk=None, gate=None, kv_heads=None, v_dim=None, keep_first=0, softcap=None, sink=None,
+                   values_in_keys=False):
     """General paged causal attention. q: [N, n_heads*head_dim] view; returns [N, n_heads*v_dim]. chunk: positions
     are cut into chunks of this many from the start of the sequence and nothing is seen across a border. gate:
     [N, n_heads] view, a head's output is multiplied by the logistic function of its entry. kv_heads and v_dim name the
-    sizes of a cache whose value heads differ from its key heads (see cache_geometry)."""
+    sizes of a cache whose value heads differ from its key heads (see cache_geometry). keep_first: behind a window, the
+    first so many keys of the sequence stay visible. softcap c: a scaled score s becomes c * tanh(s / c). sink: float32
+    [n_heads], exp(sink) joins the softmax's denominator. values_in_keys: the cache holds key rows only
+    ([pages, kv_heads * page_size * head_dim]) and a value is the first v_dim elements of its key row."""
     head_dim = q.shape[1] // n_heads
-    n_pages, kv_heads, page_size, head_dim, v_dim = cache_geometry(cache, kv_heads, head_dim, v_dim)
+    if values_in_keys:
+        kv_heads = kv_heads or 1
+        if cache.dim() != 2 or cache.shape[1] % (kv_heads * head_dim) or not v_dim or v_dim > head_dim:
+            raise KernelError("attention: a cache of key rows that hold the values needs [pages, kv_heads * page * head_dim]")
+        n_pages, page_size = cache.shape[0], cache.shape[1] // (kv_heads * head_dim)
+    else:
+        n_pages, kv_heads, page_size, head_dim, v_dim = cache_geometry(cache, kv_heads, head_dim, v_dim)
+    if sink is not None and (sink.numel() != n_heads or sink.dtype != torch.float32 or not sink.is_contiguous()):
+        raise KernelError("attention: the sink must be float32 [heads]")
     n = q.shape[0]
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != cache.dtype or not cache.is_contiguous():
         raise KernelError("attention: q does not fit the cache")
@@ -430,13 +625,14 @@ def attention_rows(q, cache, token_entry, positions, block_table, n_heads, scale
     if n_splits > 1:
         part_o = torch.empty((n * n_heads * n_splits * v_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
-    _call(library("core"), "dd_attention_rows_masked", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
+    _call(library("core"), "dd_attention_rows_sinks", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
           _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           _ptr(part_o), _ptr(part_ml), n, n_heads, kv_heads, head_dim, page_size, n_pages,
           0 if window is None else int(window), float(scale), int(n_splits), _dt(q.dtype),
           _ptr(error_flag(q.device)), _stream(), v_dim, 0 if chunk is None else int(chunk), _ptr(gate, "gate"),
-          0 if gate is None else gate.stride(0), n_kernels=2 if n_splits > 1 else 1)
+          0 if gate is None else gate.stride(0), int(keep_first or 0), float(softcap or 0.0), _ptr(sink, "sink"),
+          1 if values_in_keys else 0, n_kernels=2 if n_splits > 1 else 1)
     return out
 
 

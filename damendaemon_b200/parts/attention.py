@@ -9,7 +9,9 @@ output projection (its rows are joined to the fused projection); a rotary positi
 encoding of the mixer's own; an RMS norm over every query head and every key head before
 that rotation (one kernel does both); no keys and values of its own (the mixer then
 projects queries only and reads the cache of another stop of the run order through its own
-mask). The kernels read keys and values from the cache pages only, so
+mask); first keys that stay visible behind the window, capped scores and a sink in the softmax (a learned number per
+head in the denominator); values blended with those an earlier mixer computed for the same tokens (one learned weight,
+the blended values are what is cached). The kernels read keys and values from the cache pages only, so
 a portion of a prompt sees earlier portions exactly as a decoded token sees its context.
 """
 from __future__ import annotations
@@ -75,8 +77,16 @@ class Attention(Mixer):
         if spec.gate_weight and spec.qkv_bias:
             raise ValueError("a gated attention with projection biases is not supported")
         self.rotary = None if spec.rotary is None else lookup(POSITIONS, spec.rotary, "position encoding")(spec.rotary, weights, runtime)
+        self.sink = weights[spec.sink] if spec.sink else None
+        self.value_mix = weights[spec.value_mix] if spec.value_mix else None
+        if (spec.value_mix or spec.value_mix_source) and not spec.own_keys_values:
+            raise ValueError("values are blended only by a mixer with values of its own")
+        if spec.keep_first < 0 or (spec.softcap is not None and spec.softcap <= 0):
+            raise ValueError("keep_first must not be negative and a score cap must be positive")
         # what the attention kernels are told beside heads, scale and window
-        self.mask = dict(chunk=spec.chunk, value_dim=None if plain else self.value_dim)
+        self.mask = dict(chunk=spec.chunk, value_dim=None if plain else self.value_dim, keep_first=spec.keep_first,
+                         softcap=spec.softcap, sink=self.sink)
+        plain = plain and not spec.keep_first and not spec.softcap and self.sink is None     # the tensor-core kernels' masks
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"{spec.n_heads} heads cannot share {spec.n_kv_heads} key/value heads")
         # where this mixer likes a prompt to be cut: the key block of its prompt kernel, if that kernel takes its sizes
@@ -109,6 +119,10 @@ class Attention(Mixer):
         for name in (spec.query_norm, spec.key_norm):
             if name:
                 decls.append(TensorDecl(name, (spec.head_dim,), "vector"))
+        if spec.sink:
+            decls.append(TensorDecl(spec.sink, (spec.n_heads,), "vector"))
+        if spec.value_mix:
+            decls.append(TensorDecl(spec.value_mix, (), "vector"))
         return decls
 
     @staticmethod
@@ -118,7 +132,8 @@ class Attention(Mixer):
         value_dim = None if spec.value_dim in (None, spec.head_dim) else spec.value_dim
         # the cache keeps what the widest mask that reads it needs (other stops may read it through masks of their own)
         kept = spec.window if spec.keep_window is None else (None if spec.keep_window == "all" else int(spec.keep_window))
-        return [PagedKeyValues(spec.n_kv_heads, spec.head_dim, kept, value_dim, spec.chunk)]
+        return [PagedKeyValues(spec.n_kv_heads, spec.head_dim, kept, value_dim, spec.chunk,
+                               spec.keep_first if kept is not None or spec.chunk is not None else 0)]
 
     def forward(self, y, residual, ctx, cache, position):
         s = self.spec
@@ -146,6 +161,13 @@ class Attention(Mixer):
                 q, k = self.rotary.on_query_key(q, k, ctx)
         elif self.rotary is not None:
             q, k = self.rotary.on_query_key(q, k, ctx)
+        if s.value_mix_source:
+            ctx.shared["values_to_mix"] = v          # later mixers of this step blend their values with these
+        elif self.value_mix is not None:
+            first = ctx.shared.get("values_to_mix")
+            if first is None or first.shape != v.shape:
+                raise ValueError("values are blended with those of an earlier mixer of the same step and shape; none was left")
+            kernels.blend_rows(v, first, self.value_mix)
         attended = ctx.attend(q, k, v, cache, s.n_heads, s.scale, s.window, gate=gate, **self.mask)
         return linear(self.runtime, attended, self.out_w, self.out_b, residual=residual, out_dtype=residual.dtype,
                       out=residual)

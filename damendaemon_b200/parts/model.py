@@ -1,7 +1,11 @@
 """A decoder assembled from parts according to a ModelSpec. Architecture-agnostic."""
 from __future__ import annotations
 
-from . import attention, block, embedding, feed_forward, head, norms, positions, retention  # noqa: F401  (register the built-in parts)
+import torch
+
+from .. import kernels
+from . import attention, block, delta_rule, embedding, feed_forward, head, latent_attention, norms, positions, retention  # noqa: F401  (register the built-in parts)
+from .spec import TensorDecl
 from .registry import ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, lookup
 
 
@@ -14,7 +18,10 @@ def tensor_decls(spec):
             decls += lookup(NORMS, norm, "norm").tensor_decls(norm)
         decls += lookup(MIXERS, layer.mixer, "mixer").tensor_decls(layer.mixer)
         decls += lookup(FEED_FORWARDS, layer.feed_forward, "feed-forward").tensor_decls(layer.feed_forward)
+        decls += getattr(lookup(ARRANGEMENTS, layer, "block arrangement"), "tensor_decls", lambda _: [])(layer)
     decls += lookup(HEADS, spec.head, "head").tensor_decls(spec.head)
+    for stop, name in enumerate(spec.depth_mix or ()):
+        decls.append(TensorDecl(name, (stop + 2,), "vector"))
     unique = {}
     for d in decls:
         if d.name in unique and unique[d.name] != d:
@@ -24,11 +31,15 @@ def tensor_decls(spec):
 
 
 def cache_needs(spec):
-    """One list of cache needs per stop of the run order (empty for a stop that reads another's cache)."""
+    """One list of cache needs per stop of the run order: the mixer's (none for a stop that reads another's cache) and
+    the block arrangement's own (a state with a name)."""
     needs = []
     for entry in spec.run_order:
-        mixer = spec.layers[entry.layer].mixer
-        needs.append([] if entry.cache_of is not None else list(lookup(MIXERS, mixer, "mixer").cache_needs(mixer)))
+        layer = spec.layers[entry.layer]
+        mixer = layer.mixer
+        mine = [] if entry.cache_of is not None else list(lookup(MIXERS, mixer, "mixer").cache_needs(mixer))
+        mine += getattr(lookup(ARRANGEMENTS, layer, "block arrangement"), "cache_needs", lambda _: [])(layer)
+        needs.append(mine)
     return needs
 
 
@@ -50,9 +61,16 @@ class DecoderModel:
             feed = lookup(FEED_FORWARDS, layer.feed_forward, "feed-forward")(layer.feed_forward, weights, runtime)
             built_norms = [lookup(NORMS, norm, "norm")(norm, weights, runtime) for norm in layer.norms]
             self.blocks.append(lookup(ARRANGEMENTS, layer, "block arrangement")(layer, built_norms, mixer, feed))
+            if hasattr(self.blocks[-1], "bind"):
+                self.blocks[-1].bind(weights)           # an arrangement with tensors of its own
             self.mixers.append(mixer)
             self.feed_forwards.append(feed)
         self.head = lookup(HEADS, spec.head, "head")(spec.head, weights, runtime)
+        self.depth_mix = None
+        if spec.depth_mix is not None:
+            if len(spec.depth_mix) != len(spec.run_order):
+                raise ValueError(f"{len(spec.depth_mix)} depth weights for {len(spec.run_order)} stops of the run order")
+            self.depth_mix = [weights[name] for name in spec.depth_mix]
         self.graph_safe = all(getattr(m, "graph_safe", False) for m in self.mixers) and \
             all(getattr(f, "graph_safe", False) for f in self.feed_forwards)
         # where the mixers like a prompt to be cut (a key block of a prompt attention kernel); 1: anywhere
@@ -64,8 +82,24 @@ class DecoderModel:
         caches: per stop of the run order, the LayerCache view its mixer reads (and writes, if it is its own).
         """
         x = self.embedding.forward(ctx, self.position)
-        for stop, entry in enumerate(self.spec.run_order):
-            x = self.blocks[entry.layer].forward(x, ctx, caches[stop], self.position)
+        if self.depth_mix is not None:
+            x = self._forward_mixed_over_depth(x, ctx, caches)
+        else:
+            for stop, entry in enumerate(self.spec.run_order):
+                x = self.blocks[entry.layer].forward(x, ctx, caches[stop], self.position)
         if ctx.n_wanted == 0:
             return None
         return self.head.forward(x, ctx)
+
+    def _forward_mixed_over_depth(self, x, ctx, caches):
+        """Every stop's result stays: plane 0 of the stack is the embedding's output, plane i + 1 what stop i leaves. A stop
+        runs in place on the plane that will hold its result, which first receives what the stop reads: a copy of plane 0 for
+        the first stop, else the weighted sum of all planes so far by the weights of the stop before."""
+        stops = len(self.spec.run_order)
+        stack = torch.empty((stops + 2, *x.shape), dtype=torch.float32, device=x.device)
+        stack[0].copy_(x)
+        stack[1].copy_(x)
+        for stop, entry in enumerate(self.spec.run_order):
+            self.blocks[entry.layer].forward(stack[stop + 1], ctx, caches[stop], self.position)
+            kernels.weighted_sum(stack, self.depth_mix[stop], stop + 2, stack[stop + 2])
+        return stack[stops + 1]

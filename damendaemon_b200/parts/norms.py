@@ -1,5 +1,6 @@
 """Norms. LayerNorm with weight and optional bias (damendaemon/starcoder.py:53-55); RMS norm,
-x / sqrt(mean(x^2) + eps) * (offset + weight), with the offset a parameter of the spec."""
+x / sqrt(mean(x^2) + eps) * (offset + weight), with the offset a parameter of the spec, and optionally in groups:
+the row in equal consecutive stretches, each divided by its own root mean square."""
 from __future__ import annotations
 
 from .. import kernels
@@ -31,6 +32,8 @@ class RmsNorm(Norm):
     def __init__(self, spec, weights, runtime):
         if spec.bias:
             raise ValueError("an RMS norm has no bias")
+        if spec.groups < 1 or spec.width % spec.groups:
+            raise ValueError(f"a row of {spec.width} does not fall into {spec.groups} equal stretches")
         self.spec, self.runtime = spec, runtime
         self.weight = weights[spec.weight]
 
@@ -40,4 +43,9 @@ class RmsNorm(Norm):
 
     def forward(self, x, row_index=None, out_dtype=None):
         return kernels.rmsnorm(x, self.weight, self.spec.eps, out_dtype or self.runtime.dtype, row_index,
-                               offset=self.spec.weight_offset)
+                               offset=self.spec.weight_offset, groups=self.spec.groups)
+
+    def forward_shifted(self, x, shift, state, ctx):
+        """The norm of every row blended with the norm of the token before it (kernels.rmsnorm_shift), one kernel."""
+        return kernels.rmsnorm_shift(x, self.weight, self.spec.eps, self.runtime.dtype, shift, state, ctx.token_entry,
+                                     ctx.entry_start, ctx.entry_slot, offset=self.spec.weight_offset, groups=self.spec.groups)

@@ -35,7 +35,8 @@ def prompt_key_block(n_heads, kv_heads, head_dim, page_size, dtype):
     return 1
 
 
-def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None, gate=None, value_dim=None):
+def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None, gate=None, value_dim=None, keep_first=0,
+                    softcap=None, sink=None):
     runtime = ctx.runtime
     tune = runtime.attention_tuning
     if (k is None) != (v is None) or (k is None and cache.writable):
@@ -55,6 +56,8 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         q, k, v = packed[:3]
         gate = packed[3] if gate is not None else None
     kv, table = cache.kv, ctx.block_table(cache.group)
+    keep_first = keep_first if window is not None or chunk is not None else 0
+    more = dict(keep_first=keep_first, softcap=softcap, sink=sink)      # what only the general kernel takes
     if value_dim is not None and value_dim != cache.group.need.head_dim:
         need = cache.group.need
         # value heads of their own size: the general kernel, which is told the page's geometry
@@ -63,7 +66,13 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
                              v_dim=value_dim)
         return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
                                       n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate, kv_heads=need.kv_heads,
-                                      v_dim=value_dim)
+                                      v_dim=value_dim, **more)
+    if keep_first or softcap or sink is not None:
+        # first keys kept behind the window, capped scores, a sink in the softmax: the general kernel
+        if cache.writable:
+            kernels.kv_store(k, v, ctx.token_entry, ctx.positions, table, kv)
+        return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
+                                      n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate, **more)
     kv_heads, page_size, head_dim = kv.shape[2], kv.shape[3], kv.shape[4]
     k_new, v_new = (k, v) if cache.writable else (None, None)
     fast = runtime.attention != "rows"

@@ -42,6 +42,8 @@ class NormSpec:
     weight: str          # checkpoint names
     bias: Optional[str] = None
     weight_offset: float = 0.0   # 'rmsnorm': the factor is weight_offset + weight (1 for a weight stored around zero)
+    groups: int = 1              # 'rmsnorm': the row in this many equal consecutive stretches, each divided by its own
+                                 # root mean square (the weight spans the whole row)
 
 
 @dataclass(frozen=True)
@@ -103,6 +105,78 @@ class AttentionSpec:
     # keys kept in the cache where other stops read it through a wider mask than this mixer's own ('all': every key);
     # None: what the mixer's own window needs
     keep_window: object = None
+    # behind a window, the first so many keys of the sequence stay visible (at their true positions)
+    keep_first: int = 0
+    # c: a scaled score s becomes c * tanh(s / c)
+    softcap: Optional[float] = None
+    # checkpoint name of one number per head, [n_heads]: exp(sink) joins the softmax's denominator (a key without a
+    # value; it is neither scaled nor capped)
+    sink: Optional[str] = None
+    # values blended over layers: a mixer with value_mix_source leaves its values of the step's tokens for later mixers;
+    # one with value_mix (the checkpoint name of a single number w) replaces its values by (1 - w) v + w * those, before
+    # they are cached
+    value_mix_source: bool = False
+    value_mix: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are projections of one small latent row per token. q = W_q y, per head
+    [head_dim plain | rot_dim rotated]. W_down y = [rank | rot_dim]: the first part, RMS-normed with ``latent_norm``
+    (eps ``norm_eps``), is the latent c; the second, rotated, is a key part all heads share. Per head the plain key is
+    W_up_key c and the value W_up_value c; score = (q_plain . k_plain + q_rot . k_rot) * scale over every earlier token;
+    ``sink`` as in ``AttentionSpec``. Only c and the rotated key part are cached."""
+    kind: str            # 'latent_attention'
+    width: int
+    n_heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    rank: int
+    scale: float
+    norm_eps: float
+    rotary: object       # a RotarySpec over the rot_dim part (head_dim = rot_dim there)
+    query_weight: str    # checkpoint names; matrices [out, in]
+    down_weight: str
+    latent_norm: str
+    up_key_weight: str
+    up_value_weight: str
+    out_weight: str
+    sink: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule with a decay per key channel. q = W_q y, k = W_k y ([n_kv_heads, head_dim]), v = W_v y
+    ([n_heads, value_dim]); each passes a short causal convolution over time per channel (``conv_taps`` taps, weights
+    '<projection>.conv' [channels, taps], the last tap is the current token's) and silu; q and k become unit vectors
+    per head (x / sqrt(sum x^2 + 1e-6)), q times head_dim^-1/2; head h uses q/k head h // (n_heads / n_kv_heads).
+    beta = sigmoid(W_beta y) per head; decay = exp(-exp(A_log[head]) * softplus(W_a2 (W_a1 y) + dt_bias)) per head and
+    key channel. Per head S <- decay[:, None] * S; u = beta * (v - S^T k); S <- S + k u^T; o = S^T q, S float32 per
+    request from zero. o is divided by its root mean square per head (``norm_eps``), multiplied by ``out_norm`` [value_dim]
+    and by sigmoid(W_g2 (W_g1 y)), and projected by W_out."""
+    kind: str            # 'gated_delta'
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    value_dim: int
+    conv_taps: int
+    decay_rank: int
+    gate_rank: int
+    norm_eps: float
+    query_weight: str    # checkpoint names; matrices [out, in]
+    key_weight: str
+    value_weight: str
+    beta_weight: str
+    decay_down: str
+    decay_up: str
+    decay_log: str       # A_log [n_heads]
+    decay_bias: str      # dt_bias [n_heads * head_dim]
+    gate_down: str
+    gate_up: str
+    out_norm: str
+    out_weight: str
 
 
 @dataclass(frozen=True)
@@ -208,11 +282,14 @@ class NoFeedForwardSpec:
 class LayerSpec:
     """A layer: a mixer, a feed-forward, as many norms as its arrangement wants, and the arrangement that wires them
     ('pre_norm' takes two norms: before the mixer, before the feed-forward; 'pre_norm_mixer' one norm and no
-    feed-forward; 'parallel' one norm whose output both the mixer and the feed-forward read)."""
+    feed-forward; 'parallel' one norm whose output both the mixer and the feed-forward read; 'pre_norm_shift' is
+    'pre_norm', or 'pre_norm_mixer' with one norm, whose mixer reads its normed input blended per channel with the
+    normed input of the token before: n[t] + (n[t-1] - n[t]) * ``shift_weight`` [width], n[-1] = 0)."""
     arrangement: str
     mixer: object
     feed_forward: object
     norms: Tuple[object, ...]
+    shift_weight: Optional[str] = None
 
     @property
     def kind(self):
@@ -263,6 +340,10 @@ class ModelSpec:
     layers: Tuple[LayerSpec, ...]
     run_order: Tuple[RunEntry, ...]
     head: object                      # a head spec (with the final norm)
+    # Streams mixed over depth: None, or per stop of the run order the checkpoint name of its weights [stop + 2]. With
+    # X_0 the embedding's output and X_(i+1) what stop i leaves, what stop i + 1 (and after the last stop the head)
+    # reads is sum over j <= i + 1 of weights_i[j] * X_j
+    depth_mix: Optional[Tuple[str, ...]] = None
     eos_token_ids: Tuple[int, ...] = ()
     ignored_tensors: Tuple[str, ...] = field(default_factory=tuple)   # regexes of tensors to drop
     tied_duplicates: Tuple[Tuple[str, str], ...] = field(default_factory=tuple)  # (name, must equal)

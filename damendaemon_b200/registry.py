@@ -19,6 +19,9 @@ class Architecture:
     parse_config: Callable      # dict -> typed config
     build_spec: Callable        # typed config -> ModelSpec
     random_tensors: Callable    # (typed config, seed, matrix dtype) -> {checkpoint name: tensor}
+    # (typed config, {checkpoint name: shape}) -> typed config: for an architecture whose config.json leaves sizes to the
+    # tensors' shapes; None where config.json says everything
+    sizes_from_shapes: Callable = None
 
 
 ARCHITECTURES: dict = {}
@@ -44,11 +47,16 @@ def architecture_of(config: dict) -> Architecture:
 
 
 def load_config(model_dir):
-    """Folder -> (Architecture, typed config)."""
+    """Folder -> (Architecture, typed config); sizes that only the tensors' shapes give are read from the weight files'
+    headers."""
     raw = read_config_file(model_dir)
     arch = architecture_of(raw)
-    return arch, arch.parse_config(raw)
+    typed = arch.parse_config(raw)
+    if arch.sizes_from_shapes is not None:
+        from .weights.loader import tensor_shapes
+        typed = arch.sizes_from_shapes(typed, tensor_shapes(model_dir))
+    return arch, typed
 
 
 def _load_builtin():
-    from .architectures import bonatar, gpt2, zokanex  # noqa: F401  (register themselves on import)
+    from .architectures import bonatar, derusun, gpt2, zokanex  # noqa: F401  (register themselves on import)

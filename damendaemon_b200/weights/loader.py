@@ -63,6 +63,19 @@ def weight_file(model_dir) -> Path:
     return weight_files(model_dir)[0]
 
 
+def tensor_shapes(model_dir) -> dict:
+    """{tensor name: shape} of a model folder, from the headers of its weight files alone (no tensor is read)."""
+    shapes = {}
+    for path in weight_files(model_dir):
+        f = SafetensorsFile(path)
+        try:
+            for name in f.names():
+                shapes[name] = tuple(f.describe(name)[1])
+        finally:
+            f.close()
+    return shapes
+
+
 class ShardedSource:
     """Several safetensors files read as one; a tensor name may appear in one shard only."""
 
