@@ -1,6 +1,6 @@
 // Causal attention over the paged cache, one warp per (token, head, key split).
 // This is the general kernel: any number of heads and key/value groups, head sizes
-// in steps of 8 up to 256, an optional window, portions of prompts and single
+// up to 512 (16-byte loads where they are multiples of 8), an optional window, portions of prompts and single
 // decoded tokens in the same launch. Scores, the running maximum, the softmax sum
 // and the weighted value sum are float32 whatever the storage type
 // (damendaemon/kernels.py:133-210: scale d^-0.5, mask key <= position, exp(s - max),
@@ -284,7 +284,8 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
     if (dv <= 32) DD_ROWS(1);
     else if (dv <= 64) DD_ROWS(2);
     else if (dv <= 128) DD_ROWS(4);
-    else DD_ROWS(8);
+    else if (dv <= 256) DD_ROWS(8);
+    else DD_ROWS(16);
 #undef DD_ROWS
     if (int e = dd_check_launch("dd_attention_rows")) return e;
     if (n_splits > 1) {
@@ -317,8 +318,8 @@ DD_API int dd_attention_rows_sinks(const void* q, int q_stride, const void* cach
     if (keep_first < 0 || softcap < 0.f) return dd_fail("dd_attention_rows: keep_first %d and softcap %g must not be negative", keep_first, softcap);
     if (values_in_keys && v_dim > head_dim) return dd_fail("dd_attention_rows: a value of %d elements does not lie in a key row of %d", v_dim, head_dim);
     const RowsExtra extra = {keep_first, softcap, sink, values_in_keys ? 1 : 0};
-    if (head_dim <= 0 || head_dim > 256 || v_dim <= 0 || v_dim > 256)
-        return dd_fail("dd_attention_rows: head sizes %d and %d are not supported (at most 256)", head_dim, v_dim);
+    if (head_dim <= 0 || head_dim > 512 || v_dim <= 0 || v_dim > 512)
+        return dd_fail("dd_attention_rows: head sizes %d and %d are not supported (at most 512)", head_dim, v_dim);
     if (window < 0 || chunk < 0) return dd_fail("dd_attention_rows: window %d and chunk %d must not be negative", window, chunk);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads)
         return dd_fail("dd_attention_rows: %d heads cannot share %d key/value heads", n_heads, n_kv_heads);

@@ -260,9 +260,13 @@ DD_API int dd_delta_rule(const float* q, const float* k, const float* v, const f
     const int cols = DR_THREADS / lpc;
     const dim3 grid(dd_ceil_div(dv, cols), H, n_entries);
     const size_t smem = (size_t)(DR_TOKENS * (3 * 8 * lpc + cols + 1)) * sizeof(float);
-#define DD_RULE(L)                                                                                                     \
-    dd_launch(delta_rule_kernel<L>, grid, dim3(DR_THREADS), smem, s, q, k, v, decay, beta, entry_start, entry_slot, state, \
-              out, H, G, dk, dv)
+#define DD_RULE(L)                                                                                                      \
+    do {                                                                                                                \
+        if (smem > 48 * 1024)                                                                                           \
+            cudaFuncSetAttribute(delta_rule_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+        dd_launch(delta_rule_kernel<L>, grid, dim3(DR_THREADS), smem, s, q, k, v, decay, beta, entry_start, entry_slot,   \
+                  state, out, H, G, dk, dv);                                                                            \
+    } while (0)
     switch (lpc) {
         case 1: DD_RULE(1); break;
         case 2: DD_RULE(2); break;

@@ -125,6 +125,11 @@ rmsnorm_groups_kernel(const float* __restrict__ x, const int* __restrict__ row_i
     for (int c = threadIdx.x; c < width; c += THREADS) o[c] = dd_from_f32<TO>(in[c] * r[c / gw] * (offset + weight[c]));
 }
 
+// Explicit roundings, so that a normed value has the same bits whether it is blended at once or kept in the state first
+// (the compiler would otherwise contract the products into the subtraction in one place and not in the other).
+__device__ __forceinline__ float normed_value(float x, float r, float w) { return __fmul_rn(__fmul_rn(x, r), w); }
+__device__ __forceinline__ float blended_value(float n, float p, float mu) { return __fmaf_rn(__fsub_rn(p, n), mu, n); }
+
 template <typename TO, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ mu,
@@ -148,8 +153,8 @@ rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weig
         group_scales<THREADS>(before, width, groups, eps, r_other, scratch);
         for (int c = threadIdx.x; c < width; c += THREADS) {
             const float w = offset + weight[c];
-            const float n = in[c] * r_own[c / gw] * w, p = before[c] * r_other[c / gw] * w;
-            o[c] = dd_from_f32<TO>(n + (p - n) * mu[c]);
+            const float n = normed_value(in[c], r_own[c / gw], w), p = normed_value(before[c], r_other[c / gw], w);
+            o[c] = dd_from_f32<TO>(blended_value(n, p, mu[c]));
         }
         return;
     }
@@ -159,9 +164,9 @@ rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weig
     if (last != t) group_scales<THREADS>(tail, width, groups, eps, r_other, scratch);
     for (int c = threadIdx.x; c < width; c += THREADS) {
         const float w = offset + weight[c];
-        const float n = in[c] * r_own[c / gw] * w, p = kept[c];
-        o[c] = dd_from_f32<TO>(n + (p - n) * mu[c]);
-        kept[c] = last != t ? tail[c] * r_other[c / gw] * w : n;
+        const float n = normed_value(in[c], r_own[c / gw], w), p = kept[c];
+        o[c] = dd_from_f32<TO>(blended_value(n, p, mu[c]));
+        kept[c] = last != t ? normed_value(tail[c], r_other[c / gw], w) : n;
     }
 }
 }  // namespace

@@ -87,7 +87,7 @@ class GatedDelta(Mixer):
         output (copied where the slice does not start on a 16-byte boundary, which the tensor-core product needs)."""
         x = proj[:, start:start + rank]
         if (x.data_ptr() % 16 or rank % 8) and x.dtype == torch.bfloat16:
-            x = x.contiguous()
+            x = x.clone(memory_format=torch.contiguous_format)      # (a single row counts as contiguous wherever it starts)
         return linear(self.runtime, x, up, out_dtype=torch.float32)
 
     def forward(self, y, residual, ctx, cache, position):

@@ -30,8 +30,8 @@ class LatentAttention(Mixer):
     def __init__(self, spec, weights, runtime):
         self.spec, self.runtime = spec, runtime
         s = spec
-        if s.rank + s.rot_dim > 256 or s.rank % 8 or s.rot_dim % 8:
-            raise ValueError(f"a latent row of {s.rank} + {s.rot_dim} is not supported (multiples of 8, together at most 256)")
+        if s.rank + s.rot_dim > 512:
+            raise ValueError(f"a latent row of {s.rank} + {s.rot_dim} is not supported (together at most 512)")
         if s.rotary is None or s.rotary.dims > s.rot_dim or s.rotary.dims % 2 or not s.rotary.interleaved or s.rotary.blend is not None:
             raise ValueError("the rotated part takes a plain rotation of neighbouring pairs over at most rot_dim dimensions")
         key = s.query_weight + "+" + s.down_weight

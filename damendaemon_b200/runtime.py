@@ -25,7 +25,7 @@ class Runtime:
         prefill_chunk_size: largest prompt portion per step, 0 = up to the token budget.
         run_ahead: launch the next decode step before this step's tokens are read (see the scheduler).
         queue_timeout: seconds a request may wait for cache pages before it fails (None: no limit)."""
-        positions = _positions(model, config) or context or Engine.UNBOUNDED_CONTEXT   # a model may name no limit
+        positions = _positions(model, config, tensors) or context or Engine.UNBOUNDED_CONTEXT   # a model may name no limit
         self.engine = Engine(model, config=config, tensors=tensors, dtype=dtype, page_size=page_size,
                              max_requests=max_batch, device=device,
                              kv_tokens=kv_cache_tokens or max_batch * min(context or 10 ** 9, positions),
@@ -128,11 +128,13 @@ class Runtime:
         return [list(r.output) for r in requests]
 
 
-def _positions(model, config):
+def _positions(model, config, tensors=None):
     from .registry import architecture_of, load_config
     if config is not None:
         arch = architecture_of(config)
         typed = arch.parse_config(config)
+        if arch.sizes_from_shapes is not None:
+            typed = arch.sizes_from_shapes(typed, {n: tuple(t.shape) for n, t in (tensors or {}).items()})
     else:
         arch, typed = load_config(model)
     return arch.build_spec(typed).max_positions

@@ -25,6 +25,15 @@ from pathlib import Path
 import numpy as np
 import torch
 
+# None, or a dtype that stored activations are rounded to (what a 16-bit engine keeps between its kernels), so that a
+# test can measure how far such rounding alone moves the logits of a model
+ROUND = None
+
+
+def kept(x):
+    return x if ROUND is None else x.to(ROUND).to(x.dtype)
+
+
 _NP = {"F32": np.float32, "F64": np.float64, "F16": np.float16, "I32": np.int32, "I64": np.int64}
 
 
@@ -109,20 +118,20 @@ def channel_delta(h, w, p, m, eps):
     """The gated-delta mixer over a whole sequence. w: tensors, p: the prefix '<layer>.mix.', m: the mixer's sizes."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = silu(short_convolution(h @ w[p + "q"].T, w[p + "q.conv"])).reshape(T, G, dk)
-    k = silu(short_convolution(h @ w[p + "k"].T, w[p + "k.conv"])).reshape(T, G, dk)
-    v = silu(short_convolution(h @ w[p + "v"].T, w[p + "v.conv"])).reshape(T, H, dv)
+    q = silu(short_convolution(kept(h @ w[p + "q"].T), w[p + "q.conv"])).reshape(T, G, dk)
+    k = silu(short_convolution(kept(h @ w[p + "k"].T), w[p + "k.conv"])).reshape(T, G, dk)
+    v = silu(short_convolution(kept(h @ w[p + "v"].T), w[p + "v.conv"])).reshape(T, H, dv)
     q = unit_vectors(q) * dk ** -0.5
     k = unit_vectors(k)
     share = H // G
     q, k = q.repeat_interleave(share, dim=1), k.repeat_interleave(share, dim=1)
-    beta = torch.sigmoid(h @ w[p + "b"].T)
+    beta = torch.sigmoid(kept(h @ w[p + "b"].T))
     rate = torch.exp(w[p + "A_log"])[None, :, None]
-    step = torch.nn.functional.softplus((h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"]).reshape(T, H, dk)
+    step = torch.nn.functional.softplus(kept(h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"]).reshape(T, H, dk)
     decay = torch.exp(-rate * step)
     o, _ = delta_rule(q, k, v, beta, decay)
-    gate = torch.sigmoid((h @ w[p + "g1"].T) @ w[p + "g2"].T).reshape(T, H, dv)
-    o = rms(o, eps) * w[p + "norm"] * gate
+    gate = torch.sigmoid(kept(h @ w[p + "g1"].T) @ w[p + "g2"].T).reshape(T, H, dv)
+    o = kept(rms(o, eps) * w[p + "norm"] * gate)
     return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
@@ -169,16 +178,16 @@ def latent_attention(h, w, p, m, eps):
     T = h.shape[0]
     H, dk, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     positions = torch.arange(T)
-    q = (h @ w[p + "q"].T).reshape(T, H, dk + dr)
-    q_plain, q_turn = q[..., :dk], rotate_neighbours(q[..., dk:], positions, m["rot"]["dims"], m["rot"]["base"])
-    down = h @ w[p + "dkv"].T
-    latent = rms(down[:, :R], eps) * w[p + "dkv.norm"]
-    k_turn = rotate_neighbours(down[:, None, R:], positions, m["rot"]["dims"], m["rot"]["base"])[:, 0]
+    q = kept(h @ w[p + "q"].T).reshape(T, H, dk + dr)
+    q_plain, q_turn = q[..., :dk], kept(rotate_neighbours(q[..., dk:], positions, m["rot"]["dims"], m["rot"]["base"]))
+    down = kept(h @ w[p + "dkv"].T)
+    latent = kept(rms(down[:, :R], eps) * w[p + "dkv.norm"])
+    k_turn = kept(rotate_neighbours(down[:, None, R:], positions, m["rot"]["dims"], m["rot"]["base"])[:, 0])
     k_plain = (latent @ w[p + "uk"].T).reshape(T, H, dk)
     v = (latent @ w[p + "uv"].T).reshape(T, H, dv)
     scores = (torch.einsum("thd,shd->hts", q_plain, k_plain) + torch.einsum("thd,sd->hts", q_turn, k_turn)) * m["scale"]
     weights = softmax_with_sink(scores, visible(T), w[p + "sink"])
-    o = torch.einsum("hts,shd->thd", weights, v).reshape(T, H * dv)
+    o = kept(torch.einsum("hts,shd->thd", weights, v)).reshape(T, H * dv)
     return o @ w[p + "o"].T
 
 
@@ -188,14 +197,14 @@ def windowed_attention(h, w, p, m, eps, v_first=None):
     as they were attended to)."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, dk)
-    k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, dk)
-    v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, dv)
-    q = rms(q, eps) * w[p + "q.norm"]
-    k = rms(k, eps) * w[p + "k.norm"]
+    q = kept(h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, dk)
+    k = kept(h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, dk)
+    v = kept(h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, dv)
+    q = kept(rms(q, eps) * w[p + "q.norm"])
+    k = kept(rms(k, eps) * w[p + "k.norm"])
     if m.get("v_mix") and v_first is not None:
         lam = w[p + "vmix"]
-        v = (1 - lam) * v + lam * v_first
+        v = kept((1 - lam) * v + lam * v_first)
     share = H // G
     kk, vv = k.repeat_interleave(share, dim=1), v.repeat_interleave(share, dim=1)
     scores = torch.einsum("thd,shd->hts", q, kk) * m["scale"]
@@ -205,15 +214,15 @@ def windowed_attention(h, w, p, m, eps, v_first=None):
     mask = m.get("mask")
     see = visible(T, None if mask is None else mask["size"], 0 if mask is None else mask.get("keep_first", 0))
     weights = softmax_with_sink(scores, see, w[p + "sink"])
-    o = torch.einsum("hts,shd->thd", weights, vv).reshape(T, H * dv)
+    o = kept(torch.einsum("hts,shd->thd", weights, vv)).reshape(T, H * dv)
     return o @ w[p + "o"].T, v
 
 
 def clamped_unit(h, w, p, limit):
     """W_down (g * sigmoid(1.702 g) * (u + 1)) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit)."""
-    g = torch.clamp(h @ w[p + "gate"].T, max=limit)
-    u = torch.clamp(h @ w[p + "up"].T, min=-limit, max=limit)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1)) @ w[p + "down"].T
+    g = torch.clamp(kept(h @ w[p + "gate"].T), max=limit)
+    u = torch.clamp(kept(h @ w[p + "up"].T), min=-limit, max=limit)
+    return kept(g * torch.sigmoid(1.702 * g) * (u + 1)) @ w[p + "down"].T
 
 
 def forward(config, w, ids, return_layers=False):
@@ -226,7 +235,7 @@ def forward(config, w, ids, return_layers=False):
     v_first = None
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}.", layer["mixer"]
-        h = token_shift(grouped_norm(x, w[p + "norm1"], eps, groups), w[p + "shift"])
+        h = kept(token_shift(grouped_norm(x, w[p + "norm1"], eps, groups), w[p + "shift"]))
         if layer["type"] == "channel_delta":
             x = x + channel_delta(h, w, p + "mix.", m, eps)
         elif layer["type"] == "latent_attention":
@@ -239,9 +248,9 @@ def forward(config, w, ids, return_layers=False):
         else:
             raise ValueError(f"unknown layer type {layer['type']!r}")
         if layer["mlp"] is not None:
-            x = x + clamped_unit(grouped_norm(x, w[p + "norm2"], eps, groups), w, p + "mlp.", layer["mlp"]["limit"])
+            x = x + clamped_unit(kept(grouped_norm(x, w[p + "norm2"], eps, groups)), w, p + "mlp.", layer["mlp"]["limit"])
         results.append(x)
         x = sum(w[p + "dwa"][j] * results[j] for j in range(i + 2))
         handed.append(x)
-    logits = grouped_norm(x, w["final.norm"], eps, groups) @ w["head"].T
+    logits = kept(grouped_norm(x, w["final.norm"], eps, groups)) @ w["head"].T
     return (logits, torch.stack(handed)) if return_layers else logits
