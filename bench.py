@@ -349,6 +349,18 @@ ZOKANEX_KERNEL_PAIRS = [     # (a kernel of Zokanex, the like kernel of the clos
     ("grouped_upsilu_m2048", "grouped_up_m2048"), ("grouped_upsilu_m8", "grouped_up_m8"),
     ("grouped_score_m2048", "grouped_route_m2048"), ("grouped_score_m8", "grouped_route_m8"),
 ]
+DERUSUN_KERNEL_PAIRS = [     # (a kernel of Derusun, the like kernel of the closest model, Zokanex) at width 1600, 25 heads of 64
+    ("groupnorm_m2048", "rmsnorm_m2048"), ("groupnorm_m8", "rmsnorm_m8"), ("depthmix_m2048", None), ("depthmix_m8", None),
+    ("delta_p2_t1024", "retention_p2_t1024"), ("delta_p8_t1", "retention_p8_t1"), ("delta_p64_t1", "retention_p64_t1"),
+    ("deltaprep_p2_t1024", "headnorm_m2048"), ("deltaprep_p8_t1", "headnorm_m8"),
+    ("deltafinish_p2_t1024", "retfinish_p2_t1024"), ("deltafinish_p8_t1", "retfinish_p8_t1"),
+    ("latent_prefill_p2_t1024", "attn_prefill_p2_t1024_masked"), ("latent_decode_b8_c768", "attn_decode_b8_masked"),
+    ("latent_decode_b64_c768", "attn_decode_b64_masked"), ("latentprep_m2048", "headnorm_m2048"), ("latentprep_m8", "headnorm_m8"),
+    ("perhead_m2048", None), ("perheadup_m2048", None), ("perhead_m8", None), ("perheadup_m8", None),
+    ("sinks_prefill_p2_t1024", "attn_prefill_p2_t1024_masked"), ("sinks_decode_b8_c768", "attn_decode_rows_b8_masked"),
+    ("sinks_decode_b64_c768", "attn_decode_b64_masked"),
+    ("sinks_prefillrows_p2_t1024", "attn_prefill_p2_t1024_masked"), ("sinks_decoderows_b8_c768", "attn_decode_rows_b8_masked"),
+]
 CUDA_CORE_FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12      # nominal: 148 SMs x 128 lanes x one fused multiply-add a cycle at 1,965 MHz
 
 
@@ -378,6 +390,31 @@ def zokanex_configs(size, layers, vocab=50257):
     return out
 
 
+def derusun_configs(size, layers, vocab=50257):
+    """Zokanex (attention layers; retention layers) and Derusun models whose layers have one size: layers of the gated
+    delta rule, of attention over latent rows, of attention with kept first keys, capped scores, a sink and blended values
+    (every head its own keys), each with the clamped gated unit; and a mix of the three in which a third of the layers has
+    no feed-forward."""
+    z = DESIGN_SIZES[size]
+    out = {k: v for k, v in zokanex_configs(size, layers, vocab).items() if k in ("zokanex_attention_dense", "zokanex_retention_dense")}
+    heads = z["heads"]
+    delta = {"heads": heads, "kv_heads": heads, "dim": 64, "vdim": 64, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 256, "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 10000.0}}
+    attention = {"heads": heads, "kv_heads": heads, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0,
+                 "mask": {"size": 1024, "keep_first": 4}, "v_mix": True}
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+
+    def model(entries):
+        return {"architecture": "Derusun", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6, "groups": 2},
+                "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in entries]}
+    out["derusun_delta_dense"] = model([("channel_delta", delta, dense)] * layers)
+    out["derusun_latent_dense"] = model([("latent_attention", latent, dense)] * layers)
+    out["derusun_attention_dense"] = model([("attention", attention, dense)] * layers)
+    pattern = [("channel_delta", delta, None), ("attention", attention, dense), ("latent_attention", latent, dense)]
+    out["derusun_mixed"] = model([pattern[i % len(pattern)] for i in range(layers)])
+    return out
+
+
 def design_configs(size, layers, vocab=50257):
     """GPT-2 and two Bonatar models (dense layers only; expert layers only) whose layers have one size."""
     z = DESIGN_SIZES[size]
@@ -394,7 +431,8 @@ def design_configs(size, layers, vocab=50257):
 
 
 def design_bench(args):
-    """``--design bonatar`` (beside GPT-2) or ``--design zokanex`` (beside Bonatar, the closest model): prefill and decode
+    """``--design bonatar`` (beside GPT-2), ``--design zokanex`` (beside Bonatar, the closest model) or ``--design derusun``
+    (beside Zokanex, the closest model): prefill and decode
     throughput at equal layer sizes (random
     bfloat16 weights, a few layers), and each kernel of the new design beside the like kernel of the other, timed in a
     chain replayed from a CUDA graph over inputs that rotate through more memory than L2 holds."""
@@ -403,7 +441,8 @@ def design_bench(args):
     measured_peaks, peaks_from = peaks()
     hbm, tflops = measured_peaks["hbm_gbs"], measured_peaks["bf16_tflops"]
     layers = args.layers or 6
-    configs_of, pairs = (zokanex_configs, ZOKANEX_KERNEL_PAIRS) if args.design == "zokanex" else (design_configs, DESIGN_KERNEL_PAIRS)
+    configs_of, pairs = {"zokanex": (zokanex_configs, ZOKANEX_KERNEL_PAIRS), "derusun": (derusun_configs, DERUSUN_KERNEL_PAIRS),
+                         "bonatar": (design_configs, DESIGN_KERNEL_PAIRS)}[args.design]
     out = {"design": args.design, "layers": layers, "dtype": "bf16", "data": "synthetic", "peaks": dict(measured_peaks, source=peaks_from),
            "sizes": {}, "kernels": [],
            "note": "throughput in tokens a second on one B200, timed on the device; chunks of 1024 positions hold the whole context, "
@@ -486,7 +525,7 @@ def main():
     parser.add_argument("--case-iters", type=int, default=50)
     parser.add_argument("--case-graph", action="store_true", help="time the kernel case as launches replayed from one CUDA graph")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
-    parser.add_argument("--design", choices=("bonatar", "zokanex"), help="another design beside GPT-2 (zokanex: beside Bonatar) at equal layer sizes (prefill, decode, "
+    parser.add_argument("--design", choices=("bonatar", "zokanex", "derusun"), help="another design beside GPT-2 (zokanex: beside Bonatar; derusun: beside Zokanex) at equal layer sizes (prefill, decode, "
                         "kernel by kernel) instead of the headline bench")
     parser.add_argument("--parity", action="store_true", help="the float32 engine beside the bfloat16 one: on the benchmark's model "
                         "(logit differences, greedy agreement), or with --workload on that workload (the same requests in both)")

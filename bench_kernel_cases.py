@@ -129,6 +129,180 @@ def _retention_case(entries, length, dev, finish=False):
     return run, {"bytes": entries * H * D * D * 8 + tokens * H * D * (6 + 4), "flops": 4 * tokens * H * D * D, "fp32": True}
 
 
+def _group_norm_shift_case(rows, dev):
+    """The RMS norm in two groups of `rows` rows of the float32 stream (width 1600), each blended with the normed row of
+    the token before (requests of 256 tokens, or single tokens), into bfloat16."""
+    width = H * D
+    length = 256 if rows >= 256 else 1
+    entries = rows // length
+    copies = max(2, min(24, (300 << 20) // (rows * width * 4)))
+    xs = [torch.randn(rows, width, device=dev) for _ in range(copies)]
+    weight, shift = torch.ones(width, device=dev), torch.rand(width, device=dev)
+    state = torch.zeros(entries, width, device=dev)
+    entry = torch.arange(rows, dtype=torch.int32, device=dev) // length
+    start = torch.arange(entries + 1, dtype=torch.int32, device=dev) * length
+    slot = torch.arange(entries, dtype=torch.int32, device=dev)
+    out = torch.empty(rows, width, device=dev, dtype=torch.bfloat16)
+    run = lambda i: K.rmsnorm_shift(xs[i % copies], weight, 1e-5, torch.bfloat16, shift, state, entry, start, slot, groups=2, out=out)
+    return run, {"bytes": rows * width * 6, "flops": 7 * rows * width}
+
+
+def _depth_mix_case(rows, dev, planes=7):
+    """The weighted sum of `planes` float32 streams of `rows` rows (width 1600): what a layer in the middle of a model of
+    twelve layers hands on."""
+    width = H * D
+    copies = max(2, min(12, (300 << 20) // (rows * width * 4 * (planes + 1))))
+    stacks = [torch.randn(planes + 1, rows, width, device=dev) for _ in range(copies)]
+    w = torch.rand(planes, device=dev)
+    run = lambda i: K.weighted_sum(stacks[i % copies], w, planes, stacks[i % copies][planes])
+    return run, {"bytes": rows * width * 4 * (planes + 1), "flops": 2 * planes * rows * width}
+
+
+def _delta_case(entries, length, dev, which="rule", taps=4):
+    """The gated delta rule of `entries` requests of `length` tokens each in one step (25 heads of 64 by 64, every head
+    its own keys): 'rule' the recurrence over float32 state, 'prepare' its operands (convolutions of four taps with silu,
+    unit vectors, decay, beta), 'finish' the read-out's norm and gate. Float32 sums on the CUDA cores."""
+    tokens = entries * length
+    qk = vw = H * D
+    channels = 2 * qk + vw
+    copies = max(2, min(24, (300 << 20) // max(1, tokens * (2 * qk + vw + H * D + H) * 4 + entries * H * D * D * 4)))
+    start = torch.arange(entries + 1, dtype=torch.int32, device=dev) * length
+    slot = torch.arange(entries, dtype=torch.int32, device=dev)
+    entry = torch.arange(tokens, dtype=torch.int32, device=dev) // length
+    if which == "prepare":
+        projs = [torch.randn(tokens, channels + 64 + 64 + 32, device=dev).mul_(0.5).to(torch.bfloat16) for _ in range(copies)]
+        step_in = torch.randn(tokens, H * D, device=dev)
+        conv_w = torch.randn(channels, taps, device=dev) * 0.5
+        conv_state = torch.zeros(entries, taps - 1, channels, device=dev)
+        a_log, dt_bias = torch.full((H,), -1.0, device=dev), torch.zeros(H * D, device=dev)
+
+        def run(i):
+            p = projs[i % copies]
+            K.delta_prepare(p, p[:, channels + 128:channels + 128 + H], step_in, conv_w, conv_state, a_log, dt_bias, entry, start, slot,
+                            H, H, D, D)
+        return run, {"bytes": tokens * (channels * 2 + H * D * 4 + (channels + H * D + H) * 4), "flops": tokens * (channels * (2 * taps + 8) + 12 * H * D),
+                     "fp32": True}
+    if which == "finish":
+        os_ = [torch.randn(tokens, vw, device=dev) for _ in range(copies)]
+        gate = torch.randn(tokens, vw, device=dev)
+        weight = torch.ones(D, device=dev)
+        out = torch.empty(tokens, vw, device=dev, dtype=torch.bfloat16)
+        run = lambda i: K.delta_finish(os_[i % copies], gate, weight, H, 1e-5, torch.bfloat16, out=out)
+        return run, {"bytes": tokens * vw * 10, "flops": 12 * tokens * vw}
+    unit = lambda x: x / x.view(tokens, H, D).norm(dim=-1, keepdim=True).repeat_interleave(D, -1).view(tokens, H * D)
+    ops = []
+    for _ in range(copies):
+        q, k = unit(torch.randn(tokens, qk, device=dev)) * D ** -0.5, unit(torch.randn(tokens, qk, device=dev))
+        ops.append((q, k, torch.randn(tokens, vw, device=dev), torch.rand(tokens, H * D, device=dev) * 0.1 + 0.9,
+                    torch.rand(tokens, H, device=dev)))
+    states = [torch.zeros(entries, *K.delta_state_shape(H, D, D), device=dev) for _ in range(copies)]
+    o = torch.empty(tokens, vw, device=dev)
+    run = lambda i: K.delta_rule(*ops[i % copies], start, slot, states[i % copies], H, H, D, D, out=o)
+    return run, {"bytes": entries * H * D * D * 8 + tokens * (2 * qk + vw + H * D + H + vw) * 4, "flops": 7 * tokens * H * D * D, "fp32": True}
+
+
+RANK, ROT = 256, 64        # the latent row of the latent-attention cases: 256 + 64 rotated, heads of 64 + 64, values of 64
+
+
+def _latent_cache(batch, context, dev, copies):
+    row = RANK + ROT
+    n_pages = batch * ((context + PAGE - 1) // PAGE)
+    caches = [torch.randn(n_pages, PAGE * row, device=dev).mul_(0.3).to(torch.bfloat16) for _ in range(copies)]
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, -1)
+    return caches, table
+
+
+def _latent_attention_case(batch, length, dev, decode):
+    """Attention of 25 heads over cached latent rows of 256 + 64 (one row a token is every head's key, its first 256
+    elements every head's value): `batch` prompts of `length` tokens, or (decode) `batch` single tokens behind `length`
+    keys each."""
+    row = RANK + ROT
+    context = length
+    tokens = batch if decode else batch * length
+    copies = max(2, min(12, (300 << 20) // (batch * context * row * 2)))
+    caches, table = _latent_cache(batch, context, dev, copies)
+    q = torch.randn(tokens, H * row, device=dev).mul_(0.3).to(torch.bfloat16)
+    if decode:
+        ent = torch.arange(batch, dtype=torch.int32, device=dev)
+        pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+        splits = max(1, min(-(-(K.sm_count(dev) * 2) // (batch * H)), (context + 127) // 128, 32))
+        keys = batch * context
+    else:
+        ent = torch.arange(tokens, dtype=torch.int32, device=dev) // length
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev) % length
+        splits = 1
+        keys = batch * (length * (length + 1) // 2)
+    sink = torch.zeros(H, device=dev)
+    run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, 0.1, n_splits=splits, kv_heads=1, v_dim=RANK, sink=sink,
+                                     values_in_keys=True)
+    return run, {"bytes": batch * context * row * 2 + tokens * H * (row + RANK) * 2, "flops": 2 * keys * H * (row + RANK)}
+
+
+def _latent_prepare_case(rows, dev):
+    """A step's latent rows normed, their shared key part and the queries' rotated parts rotated, the rows written into
+    their pages (25 heads of 64 + 64, latent 256 + 64)."""
+    row, qw = RANK + ROT, H * (D + ROT)
+    copies = max(2, min(24, (300 << 20) // (rows * (qw + row) * 2)))
+    bufs = [torch.randn(rows, qw + row, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    caches, table = _latent_cache(max(1, rows // 256), min(rows, 256), dev, 1)
+    length = min(rows, 256)
+    ent = torch.arange(rows, dtype=torch.int32, device=dev) // length
+    pos = torch.arange(rows, dtype=torch.int32, device=dev) % length
+    weight = torch.ones(RANK, device=dev)
+    freqs = (10000.0 ** (-torch.arange(ROT // 2, dtype=torch.float64) * 2 / ROT)).float().to(dev)
+
+    def run(i):
+        b = bufs[i % copies]
+        K.latent_prepare(b[:, :qw], b[:, qw:], weight, 1e-5, freqs, ent, pos, table, caches[0], H, D, ROT, RANK)
+    return run, {"bytes": rows * (H * ROT * 4 + row * 4), "flops": rows * (6 * H * ROT + 5 * row)}
+
+
+def _per_head_case(rows, dev, up):
+    """Every head's piece of a row times the head's own matrix (25 heads): the plain queries of 64 through the transposed
+    key matrices to 256 (with the rotated 64 carried along), or (up) the attended latent rows of 256 to values of 64."""
+    if up:
+        x = torch.randn(rows, H * RANK, device=dev).to(torch.bfloat16)
+        w = torch.randn(H, D, RANK, device=dev).mul_(0.05).to(torch.bfloat16)
+        run = lambda i: K.per_head_linear(x, w, RANK)
+        return run, {"bytes": rows * H * (RANK + D) * 2 + w.numel() * 2, "flops": 2 * rows * H * D * RANK}
+    x = torch.randn(rows, H * (D + ROT), device=dev).to(torch.bfloat16)
+    w = torch.randn(H, RANK, D, device=dev).mul_(0.1).to(torch.bfloat16)
+    run = lambda i: K.per_head_linear(x, w, D + ROT, tail=ROT)
+    return run, {"bytes": rows * H * (D + ROT + RANK + ROT) * 2 + w.numel() * 2, "flops": 2 * rows * H * D * RANK}
+
+
+def _sinks_case(batch, length, dev, decode, kernel):
+    """Attention with a window that keeps the first keys, capped scores and a sink (25 heads of 64): prompts through the
+    mma.sync kernel or single tokens through the row decode kernel ('tensor'), or either through the general kernel
+    ('rows'). The window holds the whole context, so the same keys are read as in the plain cases."""
+    context = length
+    tokens = batch if decode else batch * length
+    copies = max(2, min(12, (300 << 20) // (batch * context * H * D * 4)))
+    caches, table = _cache_case(batch, context, dev, copies)
+    q = torch.randn(tokens, H * D, device=dev).to(torch.bfloat16)
+    kw = dict(window=1024 * ((context + 1023) // 1024), keep_first=4, softcap=30.0, sink=torch.zeros(H, device=dev))
+    if decode:
+        ent = torch.arange(batch, dtype=torch.int32, device=dev)
+        pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+        splits = max(1, min(-(-(K.sm_count(dev) * 2) // (batch * H)), (context + 127) // 128, 32))
+        work = {"bytes": batch * context * H * D * 4, "flops": 4 * batch * context * H * D}
+        if kernel == "tensor":
+            run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, n_splits=splits, exact_weights=True, **kw)
+        else:
+            run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, D ** -0.5, n_splits=splits, **kw)
+        return run, work
+    start = torch.arange(batch + 1, dtype=torch.int32, device=dev) * length
+    pos0 = torch.zeros(batch, dtype=torch.int32, device=dev)
+    work = {"bytes": batch * length * H * D * 6, "flops": batch * 4 * (length * (length + 1) // 2) * H * D}
+    if kernel == "tensor":
+        run = lambda i: K.attention_prefill(q, caches[i % copies], start, pos0, table, H, D ** -0.5, exact_weights=True, **kw)
+    else:
+        ent = torch.arange(tokens, dtype=torch.int32, device=dev) // length
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev) % length
+        run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, D ** -0.5, **kw)
+    return run, work
+
+
 def _gated_act_case(rows, dev):
     """The dense gated unit between its two products: rows of [gate | up] halves (2 x 6400) -> tanh-gelu(gate) * up."""
     inner = 6400
@@ -230,13 +404,35 @@ def build(name, device="cuda:0"):
     attn_prefill_long (one prompt of 4,096 tokens) | layernorm_m<rows> | rmsnorm_m<rows> | rotary_m<rows> |
     grouped_<up|upsilu|down|route|score>_m<tokens> (sixteen experts, two per token; upsilu: the silu form of the unit;
     score: routing by a router's scores) | headnorm_m<rows> | gatedact_m<rows> | retention_p<requests>_t<tokens> |
-    retfinish_p<requests>_t<tokens>; attention cases take the suffix _masked (a chunked mask and a gate on every head's
+    retfinish_p<requests>_t<tokens> | groupnorm_m<rows> | depthmix_m<rows> | delta_p<requests>_t<tokens> | deltaprep_p.._t.. |
+    deltafinish_p.._t.. | latent_prefill_p<prompts>_t<tokens> | latent_decode_b<batch>_c<context> | latentprep_m<rows> |
+    perhead_m<rows> | perheadup_m<rows> | sinks_prefill_p<prompts>_t<tokens> | sinks_decode_b<batch>_c<context> (and
+    sinks_prefillrows_.., sinks_decoderows_..: through the general kernel); attention cases take the suffix _masked (a chunked mask and a gate on every head's
     output)"""
     K.library("core"), K.library("tensor")
     masked = name.endswith("_masked")          # attention cases: with a chunked mask and an output gate
     if masked:
         name = name[:-len("_masked")]
     parts = name.split("_")
+    if name.startswith("groupnorm_m"):
+        return _group_norm_shift_case(int(name[len("groupnorm_m"):]), device)
+    if name.startswith("depthmix_m"):
+        return _depth_mix_case(int(name[len("depthmix_m"):]), device)
+    if parts[0] in ("delta", "deltaprep", "deltafinish") and "_p" in name:
+        entries, tokens = name.split("_p")[1].split("_t")
+        return _delta_case(int(entries), int(tokens), device, {"delta": "rule", "deltaprep": "prepare", "deltafinish": "finish"}[parts[0]])
+    if parts[0] == "latent" and parts[1] in ("prefill", "decode"):
+        # latent_prefill_p<prompts>_t<tokens> | latent_decode_b<batch>_c<context>
+        a, b = name.split("_", 2)[2][1:].replace("_t", " ").replace("_c", " ").split()
+        return _latent_attention_case(int(a), int(b), device, parts[1] == "decode")
+    if name.startswith("latentprep_m"):
+        return _latent_prepare_case(int(name[len("latentprep_m"):]), device)
+    if name.startswith("perhead_m") or name.startswith("perheadup_m"):
+        return _per_head_case(int(name.split("_m")[1]), device, name.startswith("perheadup"))
+    if parts[0] == "sinks" and parts[1] in ("prefill", "decode", "prefillrows", "decoderows"):
+        # sinks_prefill_p<prompts>_t<tokens> | sinks_decode_b<batch>_c<context>; ...rows: through the general kernel
+        a, b = name.split("_", 2)[2][1:].replace("_t", " ").replace("_c", " ").split()
+        return _sinks_case(int(a), int(b), device, parts[1].startswith("decode"), "rows" if parts[1].endswith("rows") else "tensor")
     if name.startswith("rmsnorm_m"):
         return _rmsnorm_case(int(name[len("rmsnorm_m"):]), device)
     if name.startswith("rotary_m"):

@@ -66,7 +66,7 @@ def _mixer_spec(c: DerusunConfig, i: int):
                          out_weight=p + "o", out_bias=None, value_dim=m.vdim, query_norm=p + "q.norm", key_norm=p + "k.norm",
                          head_norm_eps=c.norm_eps, keep_first=m.keep_first if m.mask_size is not None else 0,
                          softcap=m.softcap, sink=p + "sink", value_mix_source=m.v_mix and first == i,
-                         value_mix=p + "vmix" if m.v_mix and first != i else None)
+                         value_mix=p + "vmix" if m.v_mix and first != i else None, exact_weights=True)
 
 
 def _layer_spec(c: DerusunConfig, i: int):
@@ -81,8 +81,9 @@ def _layer_spec(c: DerusunConfig, i: int):
 def build_spec(c: DerusunConfig) -> ModelSpec:
     n = len(c.layers)
     first = _first_mixing_layer(c)
-    # every layer that blends values has a weight for it; the first such layer's blends with nothing and is not read
-    unused = () if first is None else (rf"l{first}\.mix\.vmix",)
+    # every layer that blends values has a weight for it; the first such layer's blends with nothing and is not read (nor
+    # would be one stored with an attention layer that does not blend)
+    unused = tuple(rf"l{i}\.mix\.vmix" for i, l in enumerate(c.layers) if l.type == "attention" and (not l.mixer.v_mix or i == first))
     return ModelSpec(
         architecture=ARCHITECTURE, vocab_size=c.vocab, width=c.width, max_positions=None,
         embedding=EmbeddingSpec("tokens", c.vocab, c.width, table="embed"),

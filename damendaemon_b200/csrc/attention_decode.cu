@@ -49,6 +49,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+// the float32 values of the two bfloat16 halves of a packed pair
+__device__ __forceinline__ float bf16_low(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_high(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 // byte offset of 16-byte chunk c of key row r in a [16][D] tile, chunks swizzled by the row
 template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
     return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
@@ -77,7 +80,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ block_table, int max_blocks, __nv_bfloat16* __restrict__ out,
                         int out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ counters, int H, int P, int n_pages, int window, float scale_log2e,
-                        int* __restrict__ error_flag, int chunk, const __nv_bfloat16* __restrict__ gate, int gate_stride) {
+                        int* __restrict__ error_flag, int chunk, const __nv_bfloat16* __restrict__ gate, int gate_stride,
+                        int keep_first, float cap_log2e, float scale_over_cap, const float* __restrict__ sink,
+                        int exact_weights) {
     constexpr int C = D / 8;            // 16-byte chunks (and lanes) per key row
     constexpr int KPL = 32 / C;         // keys per copy instruction of a warp
     constexpr int STEPS = TILE / KPL;   // copy instructions of K (and of V) per lane and stage
@@ -99,15 +104,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int pos = tok_pos[t];
     int lo = window > 0 ? max(0, pos - window + 1) : 0;
     if (chunk > 0) lo = max(lo, pos - pos % chunk);         // a chunked mask: nothing before the query's own chunk
-    const int hi = pos + 1;
-    int per = (hi - lo + n_splits - 1) / n_splits;
+    // The keys a query walks are numbered as one run: the first keys that stay visible behind the window (those the
+    // window no longer covers), then the window. Run index i is key i below n_first, else key i + skip; without kept
+    // keys the run is the window itself.
+    const int n_first = (window > 0 || chunk > 0) ? min(keep_first, lo) : 0;
+    const int skip = lo - n_first;
+    const int hi = pos + 1 - skip;
+    int per = (hi + n_splits - 1) / n_splits;
     per = (per + TILE - 1) / TILE * TILE;
-    const int k0 = lo + split * per;
+    const int k0 = split * per;
     const int k1 = min(hi, k0 + per);
+    auto key_of = [&](int run) { return run < n_first ? run : run + skip; };
     const int* bt = block_table + (size_t)(tok_entry ? tok_entry[t] : t) * max_blocks;     // no tok_entry: token t is entry t
     // (the gate is the projection's output: it is read after the wait, where the result is stored)
     float gated = 1.0f;
-    for (int blk = k0 / P + (int)threadIdx.x * 32; blk < max_blocks && blk * P < k1 + 32 * P; blk += WARPS * 32 * 32)
+    for (int blk = key_of(k0) / P + (int)threadIdx.x * 32; blk < max_blocks && blk * P < k1 + 32 * P; blk += WARPS * 32 * 32)
         asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + min(blk, max_blocks - 1)));
     const size_t head_plane = (size_t)P * D;
     const size_t page_stride = 2 * (size_t)H * head_plane;       // key/value heads = heads here
@@ -125,9 +136,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         const int base = first_key + i * WARPS * TILE;
 #pragma unroll
         for (int s = 0; s < STEPS; ++s) {
-            const int key = base + s * KPL + kg;
-            const int blk = key / P;
-            pages[s] = (key < k1 && blk < max_blocks) ? bt[blk] : -1;
+            const int run = base + s * KPL + kg;
+            const int blk = key_of(run) / P;
+            pages[s] = (run < k1 && blk < max_blocks) ? bt[blk] : -1;
         }
     };
     auto issue = [&](int i, const int* pages) {
@@ -137,10 +148,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
         for (int s = 0; s < STEPS; ++s) {
             const int row = s * KPL + kg;
-            const int key = base + row;
+            const int key = key_of(base + row);
             const uint32_t off = tile_off<D>(row, c);
             const int page = pages[s];
-            bool ok = key < k1;
+            bool ok = base + row < k1;
             if (ok && (page < 0 || page >= n_pages)) {
                 atomicOr(error_flag, k_new != nullptr && key == pos ? 2 : 4);
                 ok = false;
@@ -181,7 +192,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     int issued = 0;
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
-        const bool early = issued == i && k_new != nullptr && first_key + i * WARPS * TILE + TILE <= pos;
+        const bool early = issued == i && k_new != nullptr && first_key + i * WARPS * TILE + TILE <= pos - skip;
         if (early) {
             if (i < n_tiles) issue(i, pages[i]);
             cp_commit();
@@ -241,7 +252,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = base + nt * 8 + 2 * t4 + e;
-                const float v = key < k1 ? s[nt][e] * scale_log2e : -CUDART_INF_F;
+                // (a capped score: cap * tanh(score / cap), here in units of log 2)
+                const float sc = cap_log2e > 0.f ? cap_log2e * tanhf(s[nt][e] * scale_over_cap) : s[nt][e] * scale_log2e;
+                const float v = key < k1 ? sc : -CUDART_INF_F;
                 s[nt][e] = v;
                 mx = fmaxf(mx, v);
             }
@@ -251,7 +264,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         const float corr = exp2f(m - m_new);
         m = m_new;
         l *= corr;
-        uint32_t pf[4];
+        // The weights as the A operand of the second product. exact_weights: a weight is the sum of two bfloat16
+        // numbers, its rounding and the rounding of what that left over (together 16 bits of a float32's 24), each
+        // multiplied with the values, so that the weights are not rounded to 8 bits where a design wants them in 32.
+        uint32_t pf[4], pr[4];
         {
             const float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
             const float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
@@ -260,6 +276,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             pf[1] = 0u;
             pf[2] = g == 0 ? pack_bf16(p10, p11) : 0u;
             pf[3] = 0u;
+            pr[0] = pr[1] = pr[2] = pr[3] = 0u;
+            if (exact_weights && g == 0) {
+                pr[0] = pack_bf16(p00 - bf16_low(pf[0]), p01 - bf16_high(pf[0]));
+                pr[2] = pack_bf16(p10 - bf16_low(pf[2]), p11 - bf16_high(pf[2]));
+            }
         }
 #pragma unroll
         for (int j = 0; j < C; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
@@ -269,6 +290,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             ldmatrix_x4_trans(smem_addr(vt + tile_off<D>((mi & 1) * 8 + (lane & 7), 2 * dp + (mi >> 1))), b);
             mma_bf16(o[2 * dp], pf, b[0], b[1]);
             mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+            if (exact_weights) {
+                mma_bf16(o[2 * dp], pr, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pr, b[2], b[3]);
+            }
         }
         __syncwarp();                                   // the stage may be refilled
     }
@@ -295,11 +320,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     float L = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) L += sh_ml[w][1] > 0.f ? sh_ml[w][1] * exp2f(sh_ml[w][0] - M) : 0.f;
+    // a sink joins the sum as one more term, exp2(sink - maximum) with the maximum taken over it too, where a token's
+    // last sum is made (here without a key split, else where the splits are merged)
+    const float sink2 = sink ? sink[h] * 1.4426950408889634f : -CUDART_INF_F;
+    float with_sink = 1.f, L_all = L;
+    if (sink && n_splits == 1) {
+        const float M2 = fmaxf(M, sink2);
+        with_sink = M == -CUDART_INF_F ? 0.f : exp2f(M - M2);
+        L_all = L * with_sink + exp2f(sink2 - M2);
+    }
     for (int d = threadIdx.x; d < D; d += WARPS * 32) {
         float acc = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) acc += sh_ml[w][1] > 0.f ? sh_o[w][d] * exp2f(sh_ml[w][0] - M) : 0.f;
-        if (n_splits == 1) out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L * gated : 0.f);
+        if (n_splits == 1)
+            out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(L_all > 0.f ? acc * with_sink / L_all * gated : 0.f);
         else part_o[item * D + d] = acc;
     }
     STAMP(12);
@@ -346,6 +381,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                     acc += oo[u] * w;
                 }
         }
+        if (sink) {
+            const float M2 = fmaxf(Mx, sink2);
+            const float keep = Mx == -CUDART_INF_F ? 0.f : exp2f(Mx - M2);
+            acc *= keep;
+            Lx = Lx * keep + exp2f(sink2 - M2);
+        }
         out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(Lx > 0.f ? acc / Lx * gated : 0.f);
     }
     if (threadIdx.x == 0) counters[t * H + h] = 0;
@@ -368,13 +409,20 @@ DD_API int dd_attention_decode_supported(int n_heads, int n_kv_heads, int head_d
 // [n_tokens*heads], zero before the first launch (the kernel leaves them zero); all three only when n_splits > 1.
 // chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0). gate: null,
 // or rows of gate_stride bf16 with one element per head, whose logistic function multiplies the head's output.
-DD_API int dd_attention_decode(const void* q, int q_stride, const void* k_new, const void* v_new, void* cache,
+// dd_attention_decode_sinks takes three more: keep_first, behind a window the first so many keys of the sequence stay
+// visible (0: none); softcap c, a scaled score s becomes c * tanh(s / c) (0: none); sink, float32 [n_heads] whose
+// exponentials join the softmax's denominator (null: none); exact_weights, the softmax weights enter the product with the
+// values as two bfloat16 terms (16 bits) instead of one.
+DD_API int dd_attention_decode_sinks(const void* q, int q_stride, const void* k_new, const void* v_new, void* cache,
                                const int* tok_entry, const int* tok_pos,
                                const int* block_table, int max_blocks, void* out, int out_stride, float* part_o,
                                float* part_ml, int* counters, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                int page_size, int n_pages, int window, float scale, int n_splits, int* error_flag,
-                               void* stream, int chunk, const void* gate, int gate_stride) {
+                               void* stream, int chunk, const void* gate, int gate_stride, int keep_first, float softcap,
+                               const float* sink, int exact_weights) {
     if (n_tokens <= 0) return 0;
+    if (keep_first < 0 || softcap < 0.f) return dd_fail("dd_attention_decode: keep_first %d and softcap %g must not be negative", keep_first, softcap);
+    const float cap_log2e = softcap * 1.4426950408889634f, scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
     if (!dd_attention_decode_supported(n_heads, n_kv_heads, head_dim, DD_BF16))
         return dd_fail("dd_attention_decode: needs heads == key/value heads and head size 64 or 128 (got %d, %d, %d)",
                        n_heads, n_kv_heads, head_dim);
@@ -401,11 +449,24 @@ DD_API int dd_attention_decode(const void* q, int q_stride, const void* k_new, c
         dd_launch(attention_decode_kernel<64>, dim3(grid), dim3(WARPS * 32), RING, s, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (__nv_bfloat16*)cache,
             tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, part_o, part_ml, counters,
-            n_heads, page_size, n_pages, window, scale_log2e, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride);
+            n_heads, page_size, n_pages, window, scale_log2e, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride,
+            keep_first, cap_log2e, scale_over_cap, sink, exact_weights);
     else
         dd_launch(attention_decode_kernel<128>, dim3(grid), dim3(WARPS * 32), RING, s, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (__nv_bfloat16*)cache,
             tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, part_o, part_ml, counters,
-            n_heads, page_size, n_pages, window, scale_log2e, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride);
+            n_heads, page_size, n_pages, window, scale_log2e, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride,
+            keep_first, cap_log2e, scale_over_cap, sink, exact_weights);
     return dd_check_launch("dd_attention_decode");
+}
+
+DD_API int dd_attention_decode(const void* q, int q_stride, const void* k_new, const void* v_new, void* cache,
+                               const int* tok_entry, const int* tok_pos,
+                               const int* block_table, int max_blocks, void* out, int out_stride, float* part_o,
+                               float* part_ml, int* counters, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                               int page_size, int n_pages, int window, float scale, int n_splits, int* error_flag,
+                               void* stream, int chunk, const void* gate, int gate_stride) {
+    return dd_attention_decode_sinks(q, q_stride, k_new, v_new, cache, tok_entry, tok_pos, block_table, max_blocks, out,
+                                     out_stride, part_o, part_ml, counters, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
+                                     n_pages, window, scale, n_splits, error_flag, stream, chunk, gate, gate_stride, 0, 0.f, nullptr, 0);
 }

@@ -36,6 +36,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+__device__ __forceinline__ float bf16_low(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_high(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 // byte offset of 16-byte chunk c of row r in a tile whose rows are D bf16, chunks swizzled by the row
 template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
     return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
@@ -47,7 +49,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const int* __restrict__ entry_start, const int* __restrict__ entry_pos0, int n_entries,
                          const int* __restrict__ block_table, int max_blocks, __nv_bfloat16* __restrict__ out,
                          int out_stride, int H, int KH, int P, int n_pages, int window, float scale_log2e,
-                         int* __restrict__ error_flag, int chunk, const __nv_bfloat16* __restrict__ gate, int gate_stride) {
+                         int* __restrict__ error_flag, int chunk, const __nv_bfloat16* __restrict__ gate, int gate_stride,
+                         int keep_first, float cap_log2e, float scale_over_cap, const float* __restrict__ sink,
+                         int exact_weights) {
     constexpr int NC = D / 8;                 // 16-byte chunks per row
     constexpr int KS = D / 16;                // k-steps over the head dimension
     extern __shared__ __align__(128) uint8_t smem[];
@@ -100,7 +104,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             uint8_t* dk = sK + buf * BKV * D * 2 + tile_off<D>(r, c);
             uint8_t* dv = sV + buf * BKV * D * 2 + tile_off<D>(r, c);
             int page = -1;
-            if (key >= kv_lo && key <= pos_last) {
+            if ((key >= kv_lo || key < keep_first) && key <= pos_last) {
                 const int blk = key / P;
                 page = blk < max_blocks ? bt[blk] : -1;
                 if (page < 0 || page >= n_pages) {
@@ -118,9 +122,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             }
         }
     };
+    // The tiles a block walks: those of the first keys that stay visible behind the window (as far as the window's own
+    // tiles do not hold them), then from the tile of the first key the block's first query sees.
     const int kb_first = kv_lo / BKV * BKV;
-    const int n_tiles = (pos_last - kb_first) / BKV + 1;
-    load_kv(kb_first, 0);
+    if (window <= 0 && chunk <= 0) keep_first = 0;
+    const int n_kept = (min(keep_first, kb_first) + BKV - 1) / BKV;
+    const int n_tiles = n_kept + (pos_last - kb_first) / BKV + 1;
+    auto tile_key = [&](int j) { return j < n_kept ? j * BKV : kb_first + (j - n_kept) * BKV; };
+    load_kv(tile_key(0), 0);
     cp_commit();
 
     float o[NC][4], m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
@@ -133,8 +142,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     for (int i = 0; i < 2; ++i) qlo[i] = first_seen(qpos[i]);
 
     for (int j = 0; j < n_tiles; ++j) {
-        const int kb = kb_first + j * BKV, buf = j & 1;
-        if (j + 1 < n_tiles) load_kv(kb + BKV, buf ^ 1);
+        const int kb = tile_key(j), buf = j & 1;
+        if (j + 1 < n_tiles) load_kv(tile_key(j + 1), buf ^ 1);
         cp_commit();
         cp_wait<1>();
         __syncthreads();
@@ -171,8 +180,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             for (int i = 0; i < 4; ++i) {
                 const int key = kb + nt * 8 + 2 * t4 + (i & 1);
                 const int r = i >> 1;
-                float v = s[nt][i] * scale_log2e;
-                if (need_mask && (key > qpos[r] || key < qlo[r])) v = -CUDART_INF_F;
+                // (a capped score: cap * tanh(score / cap), in units of log 2)
+                float v = cap_log2e > 0.f ? cap_log2e * tanhf(s[nt][i] * scale_over_cap) : s[nt][i] * scale_log2e;
+                if (need_mask && (key > qpos[r] || (key < qlo[r] && key >= keep_first))) v = -CUDART_INF_F;
                 s[nt][i] = v;
                 mx[r] = fmaxf(mx[r], v);
             }
@@ -218,6 +228,22 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 mma_bf16(o[2 * dp], a, b[0], b[1]);
                 mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
             }
+            if (exact_weights) {
+                // what rounding the weights to bfloat16 left over, as a second bfloat16 term of the same product
+                uint32_t a2[4];
+                a2[0] = pack_bf16(s[2 * kk][0] - bf16_low(a[0]), s[2 * kk][1] - bf16_high(a[0]));
+                a2[1] = pack_bf16(s[2 * kk][2] - bf16_low(a[1]), s[2 * kk][3] - bf16_high(a[1]));
+                a2[2] = pack_bf16(s[2 * kk + 1][0] - bf16_low(a[2]), s[2 * kk + 1][1] - bf16_high(a[2]));
+                a2[3] = pack_bf16(s[2 * kk + 1][2] - bf16_low(a[3]), s[2 * kk + 1][3] - bf16_high(a[3]));
+#pragma unroll
+                for (int dp = 0; dp < NC / 2; ++dp) {
+                    uint32_t b[4];
+                    const int mi = lane >> 3;
+                    ldmatrix_x4_trans(smem_addr(tv + tile_off<D>(kk * 16 + (mi & 1) * 8 + (lane & 7), 2 * dp + (mi >> 1))), b);
+                    mma_bf16(o[2 * dp], a2, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], a2, b[2], b[3]);
+                }
+            }
         }
         __syncthreads();       // everyone is done with this buffer before it is filled again
     }
@@ -232,6 +258,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         const int row = warp * 16 + g + r * 8;
         if (row >= rows) continue;
         float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        if (sink) {
+            // one more term of the sum, exp2(sink - maximum), with the maximum taken over it too
+            const float s2 = sink[h] * 1.4426950408889634f, m2 = fmaxf(m[r], s2);
+            const float keep = m[r] == -CUDART_INF_F ? 0.f : exp2f(m[r] - m2);
+            inv = keep / (l[r] * keep + exp2f(s2 - m2));
+        }
         if (gate) inv *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)(row0 + row) * gate_stride + h])));
         __nv_bfloat16* dst = out + (size_t)(row0 + row) * out_stride + (size_t)h * D + 2 * t4;
 #pragma unroll
@@ -243,7 +275,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
 template <int D>
 int launch(const void* q, int q_stride, const void* cache, const int* entry_start, const int* entry_pos0, int n_entries,
            int n_tokens, const int* block_table, int max_blocks, void* out, int out_stride, int H, int KH, int P,
-           int n_pages, int window, float scale, int* error_flag, cudaStream_t s, int chunk, const void* gate, int gate_stride) {
+           int n_pages, int window, float scale, int* error_flag, cudaStream_t s, int chunk, const void* gate, int gate_stride,
+           int keep_first, float softcap, const float* sink, int exact_weights) {
     constexpr int SMEM = (BQ + 4 * BKV) * D * 2;
     static bool configured = false;
     if (!configured) {
@@ -255,7 +288,8 @@ int launch(const void* q, int q_stride, const void* cache, const int* entry_star
     dim3 grid(dd_ceil_div(n_tokens, BQ) + n_entries, H);
     dd_launch(attention_prefill_kernel<D>, dim3(grid), dim3(THREADS), SMEM, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
         entry_start, entry_pos0, n_entries, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, H, KH, P, n_pages,
-        window, scale * 1.4426950408889634f, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride);
+        window, scale * 1.4426950408889634f, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride, keep_first,
+        softcap * 1.4426950408889634f, softcap > 0.f ? scale / softcap : 0.f, sink, exact_weights);
     return dd_check_launch("dd_attention_prefill");
 }
 }  // namespace
@@ -268,12 +302,18 @@ DD_API int dd_attention_prefill_supported(int n_heads, int n_kv_heads, int head_
 // entry_start[e] .. entry_start[e+1]-1 at positions entry_pos0[e] ... ; block_table row e is its pages.
 // chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0). gate: null,
 // or rows of gate_stride bf16 with one element per head, whose logistic function multiplies the head's output.
-DD_API int dd_attention_prefill(const void* q, int q_stride, const void* cache, const int* entry_start,
+// dd_attention_prefill_sinks takes four more: keep_first, behind a window the first so many keys of the sequence stay
+// visible (0: none); softcap c, a scaled score s becomes c * tanh(s / c) (0: none); sink, float32 [n_heads] whose
+// exponentials join the softmax's denominator (null: none); exact_weights, the softmax weights enter the product with
+// the values as two bfloat16 terms (16 bits) instead of one.
+DD_API int dd_attention_prefill_sinks(const void* q, int q_stride, const void* cache, const int* entry_start,
                                 const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
                                 int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads, int head_dim,
                                 int page_size, int n_pages, int window, float scale, int* error_flag, void* stream,
-                                int chunk, const void* gate, int gate_stride) {
+                                int chunk, const void* gate, int gate_stride, int keep_first, float softcap,
+                                const float* sink, int exact_weights) {
     if (n_tokens <= 0 || n_entries <= 0) return 0;
+    if (keep_first < 0 || softcap < 0.f) return dd_fail("dd_attention_prefill: keep_first %d and softcap %g must not be negative", keep_first, softcap);
     if (!dd_attention_prefill_supported(n_heads, n_kv_heads, head_dim, DD_BF16))
         return dd_fail("dd_attention_prefill: needs head size 64 or 128 and heads a multiple of key/value heads (got %d, %d, %d)",
                        n_heads, n_kv_heads, head_dim);
@@ -283,7 +323,19 @@ DD_API int dd_attention_prefill(const void* q, int q_stride, const void* cache, 
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64)
         return launch<64>(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks, out,
-                          out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s, chunk, gate, gate_stride);
+                          out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s, chunk, gate, gate_stride,
+                          keep_first, softcap, sink, exact_weights);
     return launch<128>(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks, out,
-                       out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s, chunk, gate, gate_stride);
+                       out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s, chunk, gate, gate_stride,
+                       keep_first, softcap, sink, exact_weights);
+}
+
+DD_API int dd_attention_prefill(const void* q, int q_stride, const void* cache, const int* entry_start,
+                                const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
+                                int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads, int head_dim,
+                                int page_size, int n_pages, int window, float scale, int* error_flag, void* stream,
+                                int chunk, const void* gate, int gate_stride) {
+    return dd_attention_prefill_sinks(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks,
+                                      out, out_stride, n_heads, n_kv_heads, head_dim, page_size, n_pages, window, scale,
+                                      error_flag, stream, chunk, gate, gate_stride, 0, 0.f, nullptr, 0);
 }

@@ -47,14 +47,15 @@ class StepContext:
         return max(1, min(want, (self.split_context + keys_per_block - 1) // keys_per_block, 32))
 
     def attend(self, q, k, v, cache, n_heads, scale, window=None, chunk=None, gate=None, value_dim=None, keep_first=0,
-               softcap=None, sink=None):
+               softcap=None, sink=None, exact_weights=False):
         """Put this step's keys and values into the layer's cache pages (unless the cache is another
         stop's, ``cache.writable == False``) and run paged causal attention of the step's tokens.
         q, k, v: row views [N, heads * head_dim] of one buffer (the fused projection's output).
         chunk: the mask's chunk size; gate: a row view [N, heads] of the same buffer whose logistic function multiplies
         each head's output; value_dim: the size of a value head where it differs from a key head's; keep_first: the
         first so many keys stay visible behind a window; softcap c: a scaled score s becomes c tanh(s / c); sink: float32
-        [heads] whose exponentials join the softmax's denominator.
+        [heads] whose exponentials join the softmax's denominator; exact_weights: a tensor-core kernel does not round the
+        softmax weights to bfloat16 before they meet the values.
         Which kernel runs is decided in parts/paged_attention.py from the sizes and the runtime's tuning."""
         from ..parts.paged_attention import paged_attention
-        return paged_attention(self, q, k, v, cache, n_heads, scale, window, chunk, gate, value_dim, keep_first, softcap, sink)
+        return paged_attention(self, q, k, v, cache, n_heads, scale, window, chunk, gate, value_dim, keep_first, softcap, sink, exact_weights)

@@ -76,6 +76,8 @@ _SIGNATURES = {
         "dd_attention_prefill_supported": [_c_int] * 4,
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                 + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int],
+        "dd_attention_prefill_sinks": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
+                                      + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_void, _c_int],
         "dd_attention_prefill_tcgen05_supported": [_c_int] * 5,
         "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                         + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int],
@@ -85,6 +87,9 @@ _SIGNATURES = {
                                       _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int],
         "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
                                 _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int],
+        "dd_attention_decode_sinks": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
+                                      _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int,
+                                      _c_int, _c_float, _c_void, _c_int],
         "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 8
                            + [_c_void, _c_void, _c_int, _c_void, ctypes.c_longlong, _c_void, _c_void],
     },
@@ -878,16 +883,25 @@ def _gate_args(gate, q, n_heads, chunk):
 
 
 def attention_decode(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None,
-                     k_new=None, v_new=None, kernel="rows", chunk=None, gate=None):
+                     k_new=None, v_new=None, kernel="rows", chunk=None, gate=None, keep_first=0, softcap=None, sink=None,
+                     exact_weights=False):
     """Decode attention (one query per token) over a bfloat16 cache. kernel 'rows': a warp copies key rows 16 bytes
     at a time (see attention_decode_supported); 'pages': whole pages of a group of heads by TMA (see
     attention_decode_pages_supported). With k_new/v_new (row views of the buffer q lives in) the step's own keys and
     values are used from there and written into the cache by this kernel; otherwise they must be in the cache already.
     token_entry None: token t belongs to entry t (a step of single tokens in entry order). n_splits: into how many
     pieces a token's keys are cut; for 'pages' the most a token may get (the kernel deals them out by context length).
-    chunk, gate: as attention_rows."""
+    chunk, gate, keep_first, softcap, sink: as attention_rows; the last three, and exact_weights (the softmax weights
+    meet the values as two bfloat16 terms instead of one rounded to bfloat16), only with kernel 'rows'."""
     if kernel not in ("rows", "pages"):
         raise KernelError(f"attention_decode: unknown kernel {kernel!r}")
+    more = ()
+    if keep_first or softcap or sink is not None or exact_weights:
+        if kernel != "rows":
+            raise KernelError("attention_decode: kept first keys, capped scores, a sink and exact weights need the kernel 'rows'")
+        if sink is not None and (sink.numel() != n_heads or sink.dtype != torch.float32 or not sink.is_contiguous()):
+            raise KernelError("attention: the sink must be float32 [heads]")
+        more = (int(keep_first or 0), float(softcap or 0.0), _ptr(sink, "sink"), int(bool(exact_weights)))
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n = q.shape[0]
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
@@ -905,13 +919,13 @@ def attention_decode(q, cache, token_entry, positions, block_table, n_heads, sca
         part_o = torch.empty((n * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
         counters = _tile_counters(q.device, n * n_heads)
-    _call(library("tensor"), "dd_attention_decode" + ("_pages" if kernel == "pages" else ""), _ptr(q, "q"), q.stride(0),
+    _call(library("tensor"), "dd_attention_decode" + ("_pages" if kernel == "pages" else "_sinks" if more else ""), _ptr(q, "q"), q.stride(0),
           _ptr(k_new, "k_new"), _ptr(v_new, "v_new"),
           _ptr(cache, "cache"), _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           _ptr(part_o), _ptr(part_ml), _ptr(counters), n, n_heads, kv_heads, head_dim, page_size, n_pages,
           0 if window is None else int(window), float(scale), int(n_splits), _ptr(error_flag(q.device)), _stream(),
-          *_gate_args(gate, q, n_heads, chunk))
+          *_gate_args(gate, q, n_heads, chunk), *more)
     return out
 
 
@@ -928,7 +942,8 @@ ATTENTION_PREFILL_TCGEN05_KEY_BLOCK = 128       # keys per block of the tcgen05 
 
 
 def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, scale, window=None, out=None, kernel="mma",
-                      k_new=None, v_new=None, store_new=False, chunk=None, gate=None):
+                      k_new=None, v_new=None, store_new=False, chunk=None, gate=None, keep_first=0, softcap=None, sink=None,
+                      exact_weights=False):
     """Tensor-core attention for runs of consecutive tokens (prompt portions; a decoded token is a run of one)
     over a bfloat16 cache. entry_start: int32 [E+1], entry_pos0: int32 [E]. kernel: 'mma' (mma.sync tiles of 64
     queries, see attention_prefill_supported) or 'tcgen05' (tiles of 128 queries with TMA and TMEM accumulators,
@@ -937,9 +952,17 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
     in this step from there, in one piece per block instead of page by page. store_new: the tcgen05 kernel writes
     k_new/v_new into the cache itself (no kv_store before it); only for steps whose entries all start at a position
     that is a multiple of ATTENTION_PREFILL_TCGEN05_KEY_BLOCK (an entry that does not sets error bit 2).
-    chunk, gate: as attention_rows."""
+    chunk, gate, keep_first, softcap, sink: as attention_rows; the last three, and exact_weights (the softmax weights
+    meet the values as two bfloat16 terms instead of one rounded to bfloat16), only with kernel 'mma'."""
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n, n_entries = q.shape[0], entry_pos0.numel()
+    more = ()
+    if keep_first or softcap or sink is not None or exact_weights:
+        if kernel != "mma":
+            raise KernelError("attention_prefill: kept first keys, capped scores, a sink and exact weights need the kernel 'mma'")
+        if sink is not None and (sink.numel() != n_heads or sink.dtype != torch.float32 or not sink.is_contiguous()):
+            raise KernelError("attention: the sink must be float32 [heads]")
+        more = (int(keep_first or 0), float(softcap or 0.0), _ptr(sink, "sink"), int(bool(exact_weights)))
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
             or not cache.is_contiguous() or entry_start.numel() != n_entries + 1:
         raise KernelError("attention_prefill: q or the entry arrays do not fit the cache")
@@ -955,10 +978,10 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
     if store_new and k_new is None:
         raise KernelError("attention_prefill: store_new needs k_new and v_new")
     new_rows = (_ptr(k_new, "k_new"), _ptr(v_new, "v_new"), int(bool(store_new))) if kernel == "tcgen05" else ()
-    _call(library("tensor"), "dd_attention_prefill" + ("_tcgen05" if kernel == "tcgen05" else ""), _ptr(q, "q"), q.stride(0), *new_rows,
+    _call(library("tensor"), "dd_attention_prefill" + ("_tcgen05" if kernel == "tcgen05" else "_sinks" if more else ""), _ptr(q, "q"), q.stride(0), *new_rows,
           _ptr(cache, "cache"),
           _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_pos0, "entry_pos0", torch.int32), n_entries, n,
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           n_heads, kv_heads, head_dim, page_size, n_pages, 0 if window is None else int(window), float(scale),
-          _ptr(error_flag(q.device)), _stream(), *_gate_args(gate, q, n_heads, chunk))
+          _ptr(error_flag(q.device)), _stream(), *_gate_args(gate, q, n_heads, chunk), *more)
     return out

@@ -36,7 +36,7 @@ def prompt_key_block(n_heads, kv_heads, head_dim, page_size, dtype):
 
 
 def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None, gate=None, value_dim=None, keep_first=0,
-                    softcap=None, sink=None):
+                    softcap=None, sink=None, exact_weights=False):
     runtime = ctx.runtime
     tune = runtime.attention_tuning
     if (k is None) != (v is None) or (k is None and cache.writable):
@@ -57,7 +57,12 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         gate = packed[3] if gate is not None else None
     kv, table = cache.kv, ctx.block_table(cache.group)
     keep_first = keep_first if window is not None or chunk is not None else 0
-    more = dict(keep_first=keep_first, softcap=softcap, sink=sink)      # what only the general kernel takes
+    # first keys kept behind the window, capped scores, a sink in the softmax: the general kernel, the row decode kernel and
+    # the mma.sync prompt kernel take them; the latter two also the weights in two bfloat16 terms (the general kernel's are
+    # float32 anyway)
+    more = dict(keep_first=keep_first, softcap=softcap, sink=sink)
+    special = bool(keep_first or softcap or sink is not None or exact_weights)
+    exact = dict(more, exact_weights=exact_weights) if special else {}
     if value_dim is not None and value_dim != cache.group.need.head_dim:
         need = cache.group.need
         # value heads of their own size: the general kernel, which is told the page's geometry
@@ -67,17 +72,11 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
                                       n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate, kv_heads=need.kv_heads,
                                       v_dim=value_dim, **more)
-    if keep_first or softcap or sink is not None:
-        # first keys kept behind the window, capped scores, a sink in the softmax: the general kernel
-        if cache.writable:
-            kernels.kv_store(k, v, ctx.token_entry, ctx.positions, table, kv)
-        return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
-                                      n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate, **more)
     kv_heads, page_size, head_dim = kv.shape[2], kv.shape[3], kv.shape[4]
     k_new, v_new = (k, v) if cache.writable else (None, None)
     fast = runtime.attention != "rows"
     masked = dict(chunk=chunk, gate=gate)      # every kernel takes the chunked mask and the gate on its output
-    tensor = fast and runtime.attention != "mma"
+    tensor = fast and runtime.attention != "mma" and not special
     def wants_pages(n_tokens):
         pairs = n_tokens * n_heads
         return pairs >= tune.pages_from_pairs or pairs * ctx.split_context >= tune.pages_from_pair_keys
@@ -93,7 +92,7 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         # the decode kernel takes the new keys and values from the projection and writes them itself
         splits = ctx.key_splits(n_heads, keys_per_block=tune.row_keys_per_block, blocks_per_sm=tune.row_blocks_per_sm)
         return kernels.attention_decode(q, kv, None, ctx.positions, table, n_heads, scale, window,
-                                        n_splits=splits, k_new=k_new, v_new=v_new, **masked)
+                                        n_splits=splits, k_new=k_new, v_new=v_new, **masked, **exact)
     tcgen05 = not ctx.decode_only and tensor and \
         kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, q.dtype)
     mma = not tcgen05 and not ctx.decode_only and fast and kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype)
@@ -117,7 +116,7 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         kernels.attention_decode(q[:n1], kv, None, ctx.positions[:n1], table, n_heads, scale, window, n_splits=splits,
                                  out=out[:n1], k_new=None if k_new is None else k_new[:n1],
                                  v_new=None if v_new is None else v_new[:n1], kernel="pages" if pages else "rows",
-                                 chunk=chunk, gate=None if gate is None else gate[:n1])
+                                 chunk=chunk, gate=None if gate is None else gate[:n1], **exact)
         if n1 == ctx.n_entries:
             return out
     # the tcgen05 prompt kernel writes the cache itself when no key block of its entries mixes cached and new keys
@@ -129,6 +128,6 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
                                          out=out, kernel="tcgen05", k_new=k_new, v_new=v_new, store_new=fused_store, **masked)
     if mma:
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
-                                         out=out, **masked)
+                                         out=out, **masked, **exact)
     return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
-                                  n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate)
+                                  n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate, **(more if special else {}))

@@ -117,6 +117,9 @@ class AttentionSpec:
     # they are cached
     value_mix_source: bool = False
     value_mix: Optional[str] = None
+    # the softmax weights meet the values unrounded: a tensor-core kernel splits each into two bfloat16 terms instead of
+    # rounding it to one (the float32 kernels do so anyway)
+    exact_weights: bool = False
 
 
 @dataclass(frozen=True)

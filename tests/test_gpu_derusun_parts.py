@@ -315,6 +315,89 @@ def test_a_marked_key_at_every_edge_decides_the_output(window, keep, decode):
             assert hit == bool(seen), (pos, marked, seen)
 
 
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("H,G,d,window,keep,cap,sinks", [
+    (4, 2, 64, 100, 33, 20.0, True), (3, 3, 64, 70, 9, None, True), (2, 1, 128, 130, 70, 3.0, False), (4, 4, 64, None, 0, None, True),
+    (2, 2, 128, 64, 64, 10.0, True), (6, 2, 64, 65, 130, None, True), (2, 2, 64, 1, 1, 5.0, True)])
+def test_tensor_core_attention_with_kept_first_keys_cap_and_sink(H, G, d, window, keep, cap, sinks, exact):
+    """The mma.sync prompt kernel (whole prompt; portions that start anywhere; single tokens) and, where every head has
+    keys of its own, the row decode kernel (with and without a split of the keys, the token's own key and value taken
+    from the projection's rows and written by the kernel) against the plain pieces."""
+    from damendaemon_b200 import kernels
+    T, P = 330, 16
+    dtype = torch.bfloat16
+    q, k, v = (rnd(T, h, d, seed=s).to(dtype) for h, s in ((H, 1), (G, 2), (G, 3)))
+    sink = rnd(H, seed=4) if sinks else None
+    scale = 2.0 * d ** -0.5
+    want = plain_attention(q.double(), k.double(), v.double(), scale, window, keep, cap, None if sink is None else sink.double())
+    cache, order = paged(k, v, P, 26, 5, dtype)
+    table = i32([order + [-1] * 3])
+    kw = dict(window=window, keep_first=keep, softcap=cap, sink=None if sink is None else sink.to(DEV), exact_weights=exact)
+    assert kernels.attention_prefill_supported(H, G, d, dtype)
+    qd = q.reshape(T, H * d).to(DEV)
+    tol = 0.012 if exact else 0.03
+    got = kernels.attention_prefill(qd, cache, i32([0, T]), i32([0]), table, H, scale, **kw)
+    assert (got.cpu().double().view(T, H, d) - want).abs().max() < tol
+    for first, n in ((0, 1), (1, 2), (63, 66), (64, 64), (129, 201), (T - 1, 1), (200, 65)):
+        part = kernels.attention_prefill(qd[first:first + n], cache, i32([0, n]), i32([first]), table, H, scale, **kw)
+        assert (part.cpu().double().view(n, H, d) - want[first:first + n]).abs().max() < tol, (first, n)
+    if exact:
+        # the weights' second term takes the error below what rounding them to bfloat16 costs: against the general
+        # kernel, whose weights are float32 over the same bfloat16 cache
+        rows = kernels.attention_rows(qd, cache, i32([0] * T), i32(list(range(T))), table, H, scale, window=window, keep_first=keep,
+                                      softcap=cap, sink=kw["sink"])
+        assert (got.float() - rows.float()).abs().max() <= 2.0 ** -7 * max(1.0, rows.float().abs().max().item())
+    if H == G and kernels.attention_decode_supported(H, G, d, dtype):
+        for t in (0, 1, 15, 16, 17, 63, 64, 65, 100, 199, 200, 201, T - 1):
+            for splits in (1, 3):
+                one = kernels.attention_decode(qd[t:t + 1], cache, i32([0]), i32([t]), table, H, scale, n_splits=splits, **kw)
+                assert (one.cpu().double().view(H, d) - want[t]).abs().max() < tol, (t, splits)
+        # the token's own key and value from the projection's rows, into a page that held something else
+        t = 205
+        rows = torch.cat([q[t].reshape(-1), k[t].reshape(-1), v[t].reshape(-1)]).view(1, -1).to(DEV)
+        qr, kr, vr = rows[:, :H * d], rows[:, H * d:2 * H * d], rows[:, 2 * H * d:]
+        spoiled = cache.clone()
+        spoiled[order[t // P], :, :, t % P] = 7.0
+        one = kernels.attention_decode(qr, spoiled, None, i32([t]), table, H, scale, n_splits=2, k_new=kr, v_new=vr, **kw)
+        assert (one.cpu().double().view(H, d) - want[t]).abs().max() < tol
+        assert torch.equal(spoiled[order[t // P]], cache[order[t // P]])
+    assert kernels.read_error_flag(DEV) == 0
+
+
+@pytest.mark.parametrize("kernel", ["prompt", "decode"])
+@pytest.mark.parametrize("window,keep", [(40, 20), (16, 3), (7, 9), (33, 0), (64, 64), (65, 130)])
+def test_a_marked_key_at_every_edge_decides_the_output_of_the_tensor_core_kernels(window, keep, kernel):
+    """As above for the mma.sync prompt kernel (the query is the last row of a portion of 70) and the row decode kernel."""
+    from damendaemon_b200 import kernels
+    H, d, P = 2, 64, 16
+    for pos in (window + keep + 30, 199, 64, 300):
+        edges = {pos - window + 1: True, pos - window: pos - window < keep, pos: True, 0: keep > 0 or pos < window,
+                 keep - 1: keep > 0, keep: pos - keep < window, pos - window + 2: True, 63: pos - 63 < window or 63 < keep,
+                 64: pos - 64 < window or 64 < keep, 127: pos - 127 < window or 127 < keep}
+        for marked, seen in edges.items():
+            if not 0 <= marked <= pos:
+                continue
+            T = pos + 1
+            k, v = rnd(T, H, d, seed=1) * 0.1, rnd(T, H, d, seed=2) * 0.1
+            q = rnd(T, H, d, seed=3) * 0.1
+            k[marked] = 0.0
+            k[marked, :, 3] = 30.0
+            q[pos] = 0.0
+            q[pos, :, 3] = 30.0
+            v[marked] = torch.arange(d) + 5.0
+            cache, order = paged(k, v, P, 30, marked, torch.bfloat16)
+            table = i32([order + [-1] * 2])
+            qd = q.reshape(T, H * d).to(torch.bfloat16).to(DEV)
+            kw = dict(window=window, keep_first=keep, sink=torch.zeros(H, device=DEV), exact_weights=True)
+            if kernel == "decode":
+                out = kernels.attention_decode(qd[pos:], cache, i32([0]), i32([pos]), table, H, 1.0, n_splits=3, **kw)[0]
+            else:
+                first = max(0, pos - 69)
+                out = kernels.attention_prefill(qd[first:], cache, i32([0, T - first]), i32([first]), table, H, 1.0, **kw)[-1]
+            hit = (out.float().cpu().view(H, d) - v[marked]).abs().max().item() < 0.3
+            assert hit == bool(seen), (pos, marked, seen)
+
+
 # ------------------------------------------------------------------ attention over latent rows
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -374,8 +374,8 @@ def test_attention_prefill_tcgen05_writes_the_cache(K, heads, kv_heads, page, wi
 
 
 def test_attention_rejects_bad_sizes(K):
-    cache = torch.zeros(4, 2, 2, 16, 264, device=DEV)      # heads of more than 256
-    q = torch.zeros(1, 528, device=DEV)
+    cache = torch.zeros(4, 2, 2, 16, 520, device=DEV)      # heads of more than 512
+    q = torch.zeros(1, 1040, device=DEV)
     z = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(K.KernelError, match="head size"):
         K.attention_rows(q, cache, z, z, torch.zeros(1, 2, dtype=torch.int32, device=DEV), 2, 1.0)
