@@ -356,7 +356,9 @@ DERUSUN_KERNEL_PAIRS = [     # (a kernel of Derusun, the like kernel of the clos
     ("deltafinish_p2_t1024", "retfinish_p2_t1024"), ("deltafinish_p8_t1", "retfinish_p8_t1"),
     ("latent_prefill_p2_t1024", "attn_prefill_p2_t1024_masked"), ("latent_decode_b8_c768", "attn_decode_b8_masked"),
     ("latent_decode_b64_c768", "attn_decode_b64_masked"), ("latentprep_m2048", "headnorm_m2048"), ("latentprep_m8", "headnorm_m8"),
+    ("latent_prefillrows_p2_t1024", "attn_prefill_p2_t1024_masked"), ("latent_decoderows_b8_c768", "attn_decode_b8_masked"),
     ("perhead_m2048", None), ("perheadup_m2048", None), ("perhead_m8", None), ("perheadup_m8", None),
+    ("perheadplain_m2048", None), ("perheadupplain_m2048", None),
     ("sinks_prefill_p2_t1024", "attn_prefill_p2_t1024_masked"), ("sinks_decode_b8_c768", "attn_decode_rows_b8_masked"),
     ("sinks_decode_b64_c768", "attn_decode_b64_masked"),
     ("sinks_prefillrows_p2_t1024", "attn_prefill_p2_t1024_masked"), ("sinks_decoderows_b8_c768", "attn_decode_rows_b8_masked"),

@@ -212,10 +212,10 @@ def _latent_cache(batch, context, dev, copies):
     return caches, table
 
 
-def _latent_attention_case(batch, length, dev, decode):
+def _latent_attention_case(batch, length, dev, decode, kernel="tensor"):
     """Attention of 25 heads over cached latent rows of 256 + 64 (one row a token is every head's key, its first 256
     elements every head's value): `batch` prompts of `length` tokens, or (decode) `batch` single tokens behind `length`
-    keys each."""
+    keys each; through the tensor-core kernel or ('rows') the general one."""
     row = RANK + ROT
     context = length
     tokens = batch if decode else batch * length
@@ -233,8 +233,16 @@ def _latent_attention_case(batch, length, dev, decode):
         splits = 1
         keys = batch * (length * (length + 1) // 2)
     sink = torch.zeros(H, device=dev)
-    run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, 0.1, n_splits=splits, kv_heads=1, v_dim=RANK, sink=sink,
-                                     values_in_keys=True)
+    if kernel == "tensor":
+        start = torch.arange(batch + 1, dtype=torch.int32, device=dev) * (1 if decode else length)
+        pos0 = torch.full((batch,), context - 1 if decode else 0, dtype=torch.int32, device=dev)
+        if decode:
+            tiles = -(-batch * H // 64) + batch
+            splits = max(1, min(-(-(K.sm_count(dev) * 2) // tiles), (context + 127) // 128, 32))
+        run = lambda i: K.attention_latent(q, caches[i % copies], start, pos0, table, H, RANK, 0.1, n_splits=splits, sink=sink)
+    else:
+        run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, 0.1, n_splits=splits, kv_heads=1, v_dim=RANK,
+                                         sink=sink, values_in_keys=True)
     return run, {"bytes": batch * context * row * 2 + tokens * H * (row + RANK) * 2, "flops": 2 * keys * H * (row + RANK)}
 
 
@@ -257,17 +265,17 @@ def _latent_prepare_case(rows, dev):
     return run, {"bytes": rows * (H * ROT * 4 + row * 4), "flops": rows * (6 * H * ROT + 5 * row)}
 
 
-def _per_head_case(rows, dev, up):
+def _per_head_case(rows, dev, up, kernel=None):
     """Every head's piece of a row times the head's own matrix (25 heads): the plain queries of 64 through the transposed
     key matrices to 256 (with the rotated 64 carried along), or (up) the attended latent rows of 256 to values of 64."""
     if up:
         x = torch.randn(rows, H * RANK, device=dev).to(torch.bfloat16)
         w = torch.randn(H, D, RANK, device=dev).mul_(0.05).to(torch.bfloat16)
-        run = lambda i: K.per_head_linear(x, w, RANK)
+        run = lambda i: K.per_head_linear(x, w, RANK, kernel=kernel)
         return run, {"bytes": rows * H * (RANK + D) * 2 + w.numel() * 2, "flops": 2 * rows * H * D * RANK}
     x = torch.randn(rows, H * (D + ROT), device=dev).to(torch.bfloat16)
     w = torch.randn(H, RANK, D, device=dev).mul_(0.1).to(torch.bfloat16)
-    run = lambda i: K.per_head_linear(x, w, D + ROT, tail=ROT)
+    run = lambda i: K.per_head_linear(x, w, D + ROT, tail=ROT, kernel=kernel)
     return run, {"bytes": rows * H * (D + ROT + RANK + ROT) * 2 + w.numel() * 2, "flops": 2 * rows * H * D * RANK}
 
 
@@ -421,14 +429,15 @@ def build(name, device="cuda:0"):
     if parts[0] in ("delta", "deltaprep", "deltafinish") and "_p" in name:
         entries, tokens = name.split("_p")[1].split("_t")
         return _delta_case(int(entries), int(tokens), device, {"delta": "rule", "deltaprep": "prepare", "deltafinish": "finish"}[parts[0]])
-    if parts[0] == "latent" and parts[1] in ("prefill", "decode"):
-        # latent_prefill_p<prompts>_t<tokens> | latent_decode_b<batch>_c<context>
+    if parts[0] == "latent" and parts[1] in ("prefill", "decode", "prefillrows", "decoderows"):
+        # latent_prefill_p<prompts>_t<tokens> | latent_decode_b<batch>_c<context>; ...rows: through the general kernel
         a, b = name.split("_", 2)[2][1:].replace("_t", " ").replace("_c", " ").split()
-        return _latent_attention_case(int(a), int(b), device, parts[1] == "decode")
+        return _latent_attention_case(int(a), int(b), device, parts[1].startswith("decode"), "rows" if parts[1].endswith("rows") else "tensor")
     if name.startswith("latentprep_m"):
         return _latent_prepare_case(int(name[len("latentprep_m"):]), device)
-    if name.startswith("perhead_m") or name.startswith("perheadup_m"):
-        return _per_head_case(int(name.split("_m")[1]), device, name.startswith("perheadup"))
+    if parts[0] in ("perhead", "perheadup", "perheadplain", "perheadupplain"):
+        # perhead_m<rows> | perheadup_m<rows>; ...plain: the kernel without tensor cores
+        return _per_head_case(int(name.split("_m")[1]), device, parts[0].startswith("perheadup"), "plain" if parts[0].endswith("plain") else None)
     if parts[0] == "sinks" and parts[1] in ("prefill", "decode", "prefillrows", "decoderows"):
         # sinks_prefill_p<prompts>_t<tokens> | sinks_decode_b<batch>_c<context>; ...rows: through the general kernel
         a, b = name.split("_", 2)[2][1:].replace("_t", " ").replace("_c", " ").split()

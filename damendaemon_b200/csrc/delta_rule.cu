@@ -9,7 +9,7 @@
 // a prompt and a single token run the same instructions in the same order, so a prompt cut anywhere gives the same
 // bits.
 //
-// dd_delta_prepare makes the recurrence's operands, one block a token, all float32 inside: q, k and v pass a short
+// dd_delta_prepare makes the recurrence's operands, a row of blocks a token, all float32 inside: q, k and v pass a short
 // causal convolution over time per channel (taps [channels, n], the last tap is the current token's; the n - 1 inputs
 // before a step's first token come from the request's state) and silu; q and k are made unit vectors per head
 // (x / sqrt(sum x^2 + 1e-6)), q times dk^-1/2; beta = sigmoid(b); g = exp(-exp(A_log[head]) * softplus(a + dt_bias)).
@@ -29,7 +29,9 @@ delta_prepare_kernel(const T* __restrict__ proj, int proj_stride, const T* __res
                      const int* __restrict__ tok_entry, const int* __restrict__ entry_start, const int* __restrict__ entry_slot,
                      float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out,
                      float* __restrict__ decay_out, float* __restrict__ beta_out, int H, int G, int dk, int dv) {
-    extern __shared__ float act[];                  // q and k channels after convolution and silu
+    // A token's work is dealt out over the gridDim.y blocks of its row: the value channels, decays and step sizes element
+    // by element over all their threads, the head vectors of q and k a warp each (convolution, silu and the unit norm stay
+    // inside the warp). An element is computed by the same instructions wherever it lands.
     dd_launch_dependents();
     const int t = blockIdx.x;
     const int e = tok_entry[t];
@@ -37,7 +39,7 @@ delta_prepare_kernel(const T* __restrict__ proj, int proj_stride, const T* __res
     const int qk = G * dk, C = 2 * qk + H * dv;
     const float* before = conv_state + (size_t)entry_slot[e] * (taps - 1) * C;
     dd_grid_wait();
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    auto conv = [&](int c) {
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {
             const int back = taps - 1 - j;          // tap j reads the input `back` tokens ago
@@ -45,30 +47,39 @@ delta_prepare_kernel(const T* __restrict__ proj, int proj_stride, const T* __res
                                         : before[(size_t)(taps - 1 + at - back) * C + c];
             acc = fmaf(conv_w[(size_t)c * taps + j], in, acc);
         }
-        const float y = acc * dr_sigmoid(acc);
-        if (c < 2 * qk) act[c] = y;
-        else v_out[(size_t)t * H * dv + (c - 2 * qk)] = y;
-    }
-    for (int i = threadIdx.x; i < H * dk; i += blockDim.x) {
-        const int h = i / dk;
-        decay_out[(size_t)t * H * dk + i] = expf(-expf(a_log[h]) * dr_softplus(step_in[(size_t)t * H * dk + i] + dt_bias[i]));
-    }
-    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        return acc * dr_sigmoid(acc);
+    };
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
+#pragma unroll 4
+    for (int i = first; i < H * dv; i += stride) v_out[(size_t)t * H * dv + i] = conv(2 * qk + i);
+#pragma unroll 4
+    for (int i = first; i < H * dk; i += stride)
+        decay_out[(size_t)t * H * dk + i] = expf(-expf(a_log[i / dk]) * dr_softplus(step_in[(size_t)t * H * dk + i] + dt_bias[i]));
+    for (int h = first; h < H; h += stride)
         beta_out[(size_t)t * H + h] = dr_sigmoid(dd_to_f32(beta_in[(size_t)t * beta_stride + h]));
-    __syncthreads();
-    // unit vectors: a warp a head of q or k
+    // unit vectors: a warp a head of q or k; a lane's first four elements stay in registers, further ones are computed again
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const float q_scale = 1.0f / sqrtf((float)dk);
-    for (int vec = warp; vec < 2 * G; vec += warps) {
-        const float* x = act + (size_t)vec * dk;
-        float ss = 0.f;
-        for (int i = lane; i < dk; i += 32) ss = fmaf(x[i], x[i], ss);
+    for (int vec = blockIdx.y * warps + warp; vec < 2 * G; vec += gridDim.y * warps) {
+        const int c0 = vec * dk;
+        float y[4], ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) y[r] = lane + 32 * r < dk ? conv(c0 + lane + 32 * r) : 0.f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) ss = fmaf(y[r], y[r], ss);
+        for (int i = lane + 128; i < dk; i += 32) {
+            const float x = conv(c0 + i);
+            ss = fmaf(x, x, ss);
+        }
         ss = dd_warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss + 1e-6f);
         const bool is_q = vec < G;
         float* dst = is_q ? q_out + (size_t)t * qk + (size_t)vec * dk : k_out + (size_t)t * qk + (size_t)(vec - G) * dk;
         const float f = is_q ? inv * q_scale : inv;
-        for (int i = lane; i < dk; i += 32) dst[i] = x[i] * f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (lane + 32 * r < dk) dst[lane + 32 * r] = y[r] * f;
+        for (int i = lane + 128; i < dk; i += 32) dst[i] = conv(c0 + i) * f;
     }
 }
 
@@ -213,17 +224,16 @@ DD_API int dd_delta_prepare(const void* proj, int proj_stride, const void* beta_
                             void* stream) {
     if (n <= 0) return 0;
     if (taps < 1 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0) return dd_fail("dd_delta_prepare: bad sizes");
-    const size_t smem = (size_t)2 * G * dk * sizeof(float);
-    if (smem > 200 * 1024) return dd_fail("dd_delta_prepare: %d key channels are more than a block holds", 2 * G * dk);
     cudaStream_t s = (cudaStream_t)stream;
+    // few tokens: a token's row of blocks grows until the GPU is filled (every thread keeps at least one element)
+    const int most = (int)dd_ceil_div((long long)H * (dv + dk), 256);
+    int chunks = 1;
+    while (chunks < most && (long long)n * chunks < 592) chunks *= 2;
+    chunks = chunks < most ? chunks : most;
 #define DD_PREP(T)                                                                                                        \
-    do {                                                                                                                  \
-        if (smem > 48 * 1024)                                                                                             \
-            cudaFuncSetAttribute(delta_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-        dd_launch(delta_prepare_kernel<T>, dim3(n), dim3(256), smem, s, (const T*)proj, proj_stride, (const T*)beta_in,     \
-                  beta_stride, step_in, conv_w, taps, conv_state, a_log, dt_bias, tok_entry, entry_start, entry_slot, q_out, \
-                  k_out, v_out, decay_out, beta_out, H, G, dk, dv);                                                       \
-    } while (0)
+    dd_launch(delta_prepare_kernel<T>, dim3(n, chunks), dim3(256), 0, s, (const T*)proj, proj_stride, (const T*)beta_in,    \
+              beta_stride, step_in, conv_w, taps, conv_state, a_log, dt_bias, tok_entry, entry_start, entry_slot, q_out,   \
+              k_out, v_out, decay_out, beta_out, H, G, dk, dv)
     if (dtype == DD_F32) DD_PREP(float);
     else if (dtype == DD_BF16) DD_PREP(__nv_bfloat16);
     else return dd_fail("dd_delta_prepare: unknown dtype %d", dtype);

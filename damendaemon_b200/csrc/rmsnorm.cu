@@ -94,17 +94,32 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index, c
 }
 constexpr int MAX_GROUPS = 64;
 
-// The inverse root mean squares of a row's stretches into r[0 .. groups) (shared memory); every thread sees them after.
+// The inverse root mean squares of the stretches of row a into ra[0 .. groups), and of row b (if any) into rb (shared
+// memory); every thread sees them after. A stretch is cut into 8 / groups pieces (at least one), a warp sums a piece, lane
+// by lane in a fixed order, and one thread adds a stretch's pieces: the sum of a row does not depend on which of the two
+// rows it is, nor on what the other one is.
 template <int THREADS>
-__device__ __forceinline__ void group_scales(const float* __restrict__ in, int width, int groups, float eps, float* r,
-                                             float* scratch) {
-    const int gw = width / groups;
-    for (int g = 0; g < groups; ++g) {
-        const float* part = in + (size_t)g * gw;
+__device__ __forceinline__ void group_scales(const float* __restrict__ a, float* ra, const float* __restrict__ b, float* rb,
+                                             int width, int groups, float eps, float* partial) {
+    const int gw = width / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pieces = groups >= 8 ? 1 : 8 / groups, piece = (gw + pieces - 1) / pieces;
+    const int per_row = groups * pieces, items = b ? 2 * per_row : per_row;
+    for (int it = warp; it < items; it += THREADS / 32) {
+        const int within = it % per_row, g = within / pieces, lo = (within % pieces) * piece, hi = min(gw, lo + piece);
+        const float* part = (it >= per_row ? b : a) + (size_t)g * gw;
         float sq = 0.f;
-        for (int c = threadIdx.x; c < gw; c += THREADS) sq = fmaf(part[c], part[c], sq);
-        const float total = rms_block_sum<THREADS>(sq, scratch);
-        if (threadIdx.x == 0) r[g] = 1.0f / sqrtf(total / (float)gw + eps);
+#pragma unroll 4
+        for (int c = lo + lane; c < hi; c += 32) sq = fmaf(part[c], part[c], sq);
+        sq = dd_warp_sum(sq);
+        if (lane == 0) partial[it] = sq;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < (b ? 2 : 1) * groups; i += THREADS) {
+        const int g = i % groups;
+        const float* mine = partial + (i >= groups ? per_row : 0) + g * pieces;
+        float total = 0.f;
+        for (int j = 0; j < pieces; ++j) total += mine[j];
+        (i >= groups ? rb : ra)[g] = 1.0f / sqrtf(total / (float)gw + eps);
     }
     __syncthreads();
 }
@@ -113,14 +128,14 @@ template <typename TO, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_groups_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ weight,
                       TO* __restrict__ out, int width, int groups, float eps, float offset) {
-    __shared__ float scratch[THREADS / 32];
+    __shared__ float partial[2 * MAX_GROUPS];
     __shared__ float r[MAX_GROUPS];
     dd_launch_dependents();
     dd_grid_wait();
     const int row = blockIdx.x;
     const float* in = x + (size_t)(row_index ? row_index[row] : row) * width;
     TO* o = out + (size_t)row * width;
-    group_scales<THREADS>(in, width, groups, eps, r, scratch);
+    group_scales<THREADS>(in, r, nullptr, nullptr, width, groups, eps, partial);
     const int gw = width / groups;
     for (int c = threadIdx.x; c < width; c += THREADS) o[c] = dd_from_f32<TO>(in[c] * r[c / gw] * (offset + weight[c]));
 }
@@ -135,7 +150,7 @@ __global__ void __launch_bounds__(THREADS)
 rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ mu,
                      float* __restrict__ state, const int* __restrict__ tok_entry, const int* __restrict__ entry_start,
                      const int* __restrict__ entry_slot, TO* __restrict__ out, int width, int groups, float eps, float offset) {
-    __shared__ float scratch[THREADS / 32];
+    __shared__ float partial[2 * MAX_GROUPS];
     __shared__ float r_own[MAX_GROUPS], r_other[MAX_GROUPS];
     dd_launch_dependents();
     const int t = blockIdx.x;
@@ -146,11 +161,10 @@ rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weig
     const float* in = x + (size_t)t * width;
     const int gw = width / groups;
     TO* o = out + (size_t)t * width;
-    group_scales<THREADS>(in, width, groups, eps, r_own, scratch);
     if (t != first) {
         // the token before lies in this step: its normed row again, by the same arithmetic
         const float* before = in - width;
-        group_scales<THREADS>(before, width, groups, eps, r_other, scratch);
+        group_scales<THREADS>(in, r_own, before, r_other, width, groups, eps, partial);
         for (int c = threadIdx.x; c < width; c += THREADS) {
             const float w = offset + weight[c];
             const float n = normed_value(in[c], r_own[c / gw], w), p = normed_value(before[c], r_other[c / gw], w);
@@ -161,7 +175,7 @@ rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weig
     // the first token of its entry in this step: the row before it is the state's; then the state becomes the entry's
     // last normed row (a thread writes only the channels it has read)
     const float* tail = x + (size_t)last * width;
-    if (last != t) group_scales<THREADS>(tail, width, groups, eps, r_other, scratch);
+    group_scales<THREADS>(in, r_own, last != t ? tail : nullptr, r_other, width, groups, eps, partial);
     for (int c = threadIdx.x; c < width; c += THREADS) {
         const float w = offset + weight[c];
         const float n = normed_value(in[c], r_own[c / gw], w), p = kept[c];

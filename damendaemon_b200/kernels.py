@@ -78,6 +78,11 @@ _SIGNATURES = {
                                 + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int],
         "dd_attention_prefill_sinks": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                       + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_void, _c_int],
+        "dd_attention_latent_supported": [_c_int] * 3,
+        "dd_attention_latent": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int,
+                                _c_void, _c_void] + [_c_int] * 5 + [_c_float, _c_int, _c_void, _c_void, _c_void],
+        "dd_per_head_mma_supported": [_c_int] * 6,
+        "dd_per_head_mma": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int] + [_c_int] * 5 + [_c_void],
         "dd_attention_prefill_tcgen05_supported": [_c_int] * 5,
         "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                         + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int],
@@ -452,11 +457,12 @@ def latent_prepare(q, down, weight, eps, freqs, token_entry, positions, block_ta
           _ptr(cache), cache.shape[0], cache.shape[1] // row, n, _dt(q.dtype), _ptr(error_flag(q.device)), _stream())
 
 
-def per_head_linear(x, w, in_head, out_head=None, tail=0, out=None):
+def per_head_linear(x, w, in_head, out_head=None, tail=0, out=None, kernel=None):
     """out[t, h, :J] = w[h] @ x[t, h, :I], out[t, h, J:J+tail] = x[t, h, I:I+tail]: every head's piece of a row times the
     head's own matrix. x: a row view whose head h starts at h * in_head; w: [heads, J, I] contiguous, x's type; out: rows
     whose head h starts at h * out_head (default J + tail, packed). float32 sums in an order that does not depend on the
-    batch."""
+    batch. kernel: 'mma' (bfloat16 on the tensor cores, tiles of 64 tokens x 128 outputs), 'plain', or None for 'mma'
+    where the sizes allow it."""
     heads, J, I = w.shape
     out_head = J + tail if out_head is None else out_head
     n = x.shape[0]
@@ -464,8 +470,47 @@ def per_head_linear(x, w, in_head, out_head=None, tail=0, out=None):
         raise KernelError("per_head_linear: shapes do not fit")
     if out is None:
         out = torch.empty((n, heads * out_head), dtype=x.dtype, device=x.device)
+    if kernel is None:
+        kernel = "mma" if x.dtype == torch.bfloat16 and bool(library("tensor").dd_per_head_mma_supported(
+            x.stride(0), int(in_head), out.stride(0), int(out_head), I, BF16)) else "plain"
+    if kernel == "mma":
+        _call(library("tensor"), "dd_per_head_mma", _ptr(x, "x"), x.stride(0), int(in_head), _ptr(w, "w"), _ptr(out, "out"),
+              out.stride(0), int(out_head), n, heads, I, J, int(tail), _stream())
+        return out
     _call(library("core"), "dd_per_head_linear", _ptr(x, "x"), x.stride(0), int(in_head), _ptr(w, "w"), _ptr(out, "out"),
           out.stride(0), int(out_head), n, heads, I, J, int(tail), _dt(x.dtype), _stream())
+    return out
+
+
+def attention_latent_supported(row, v_dim, dtype):
+    return dtype == torch.bfloat16 and bool(library("tensor").dd_attention_latent_supported(row, v_dim, BF16))
+
+
+def attention_latent(q, cache, entry_start, entry_pos0, block_table, n_heads, v_dim, scale, n_splits=1, sink=None, out=None):
+    """Tensor-core causal attention of runs of consecutive tokens over cached latent rows: the cache
+    ([pages, page_size * row] bfloat16) holds one row a token, which is every head's key, and whose first v_dim elements
+    are the value. q: [N, n_heads * row] row view; entry_start int32 [E+1], entry_pos0 int32 [E]; block_table row e is
+    entry e's pages. sink: float32 [n_heads], exp(sink) joins the softmax's denominator. n_splits: into how many pieces
+    a row's keys are cut (partial sums merged by a second kernel). Returns [N, n_heads * v_dim]. The softmax weights meet
+    the values as two bfloat16 terms. See attention_latent_supported for the sizes."""
+    n, n_entries = q.shape[0], entry_pos0.numel()
+    row = q.shape[1] // n_heads
+    if q.shape[1] != n_heads * row or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or \
+            cache.dim() != 2 or cache.shape[1] % row or not cache.is_contiguous() or entry_start.numel() != n_entries + 1:
+        raise KernelError("attention_latent: q or the entry arrays do not fit the cache")
+    if sink is not None and (sink.numel() != n_heads or sink.dtype != torch.float32 or not sink.is_contiguous()):
+        raise KernelError("attention: the sink must be float32 [heads]")
+    if out is None:
+        out = torch.empty((n, n_heads * v_dim), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((n * n_heads * n_splits * v_dim,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
+    _call(library("tensor"), "dd_attention_latent", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
+          _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_pos0, "entry_pos0", torch.int32), n_entries, n,
+          _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
+          _ptr(part_o), _ptr(part_ml), n_heads, row, int(v_dim), cache.shape[1] // row, cache.shape[0], float(scale),
+          int(n_splits), _ptr(error_flag(q.device)), _ptr(sink, "sink"), _stream(), n_kernels=2 if n_splits > 1 else 1)
     return out
 
 

@@ -6,7 +6,8 @@ parts, and writes the token's row [normed latent | rotated key part] straight in
 the cache keeps. The plain part of a score, q . (W_uk c), is computed as (W_uk^T q) . c: every head's plain query is
 taken through its own transposed key matrix (``kernels.per_head_linear``), so the attention runs over the cached rows
 as they are, with one shared key/value "head" whose values are the first ``rank`` elements of its keys, and a sink in
-the softmax. The result, a weighted sum of latent rows per head, becomes the head's value through W_uv (the same
+the softmax: in bfloat16 on the tensor cores (``kernels.attention_latent``: a tile's query rows are (token, head) pairs
+that share every key tile), in float32 or at sizes that kernel does not take on the general kernel. The result, a weighted sum of latent rows per head, becomes the head's value through W_uv (the same
 per-head product), then the output projection adds into the stream in its epilogue. The transposed key matrices
 [heads, rank, head_dim] are made once, when the part is built.
 """
@@ -78,8 +79,15 @@ class LatentAttention(Mixer):
                                cache.kv, s.n_heads, s.head_dim, s.rot_dim, s.rank)
         # every head's query against the cached rows: [W_uk^T q_plain | q_rotated]
         q_rows = kernels.per_head_linear(q, self.key_t, s.head_dim + s.rot_dim, tail=s.rot_dim)
-        mixed = kernels.attention_rows(q_rows, cache.kv, ctx.token_entry, ctx.positions, table, s.n_heads, s.scale,
-                                       n_splits=ctx.key_splits(s.n_heads), kv_heads=1, v_dim=s.rank, sink=self.sink,
-                                       values_in_keys=True)
+        if self.runtime.attention != "rows" and kernels.attention_latent_supported(s.rank + s.rot_dim, s.rank, q_rows.dtype):
+            # tensor-core tiles of 64 (token, head) pairs; a step of single tokens cuts its keys so that the GPU fills
+            tiles = -(-ctx.n_tokens * s.n_heads // 64) + ctx.n_entries
+            splits = max(1, min(-(-2 * ctx.sm_count // tiles), -(-ctx.split_context // 128), 32)) if ctx.decode_only else 1
+            mixed = kernels.attention_latent(q_rows, cache.kv, ctx.entry_start, ctx.entry_pos0, table, s.n_heads, s.rank,
+                                             s.scale, n_splits=splits, sink=self.sink)
+        else:
+            mixed = kernels.attention_rows(q_rows, cache.kv, ctx.token_entry, ctx.positions, table, s.n_heads, s.scale,
+                                           n_splits=ctx.key_splits(s.n_heads), kv_heads=1, v_dim=s.rank, sink=self.sink,
+                                           values_in_keys=True)
         attended = kernels.per_head_linear(mixed, self.value_up, s.rank)
         return linear(self.runtime, attended, self.out_w, residual=residual, out_dtype=residual.dtype, out=residual)

@@ -484,6 +484,90 @@ def test_a_far_latent_row_among_hundreds_is_found():
         assert (got - want).abs().max() < 2e-2, marked
 
 
+@pytest.mark.parametrize("H,R,dr,splits", [(5, 48, 16, 1), (25, 256, 64, 1), (3, 320, 32, 3), (7, 448, 64, 2), (2, 16, 16, 4), (16, 80, 48, 1)])
+def test_tensor_core_attention_over_latent_rows_against_the_general_kernel(H, R, dr, splits):
+    """Three requests side by side on shuffled pages: a portion that starts inside a page behind 70 cached rows, a prompt
+    from its start, and a single token behind 200 rows; then the same single token with its keys cut into splits."""
+    from damendaemon_b200 import kernels
+    P, row = 16, R + dr
+    held, new = [70, 0, 200], [45, 130, 1]
+    n_pages = sum(-(-(a + b) // P) for a, b in zip(held, new)) + 3
+    pages = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3)).tolist()
+    cache = torch.full((n_pages, P * row), float("nan"), dtype=torch.bfloat16, device=DEV)
+    width = max(-(-(a + b) // P) for a, b in zip(held, new)) + 1
+    table = []
+    for e, (a, b) in enumerate(zip(held, new)):
+        mine = [pages.pop() for _ in range(-(-(a + b) // P))]
+        table.append(mine + [-1] * (width - len(mine)))
+        rows = (rnd(a + b, row, seed=10 + e) * 0.7).to(torch.bfloat16).to(DEV)
+        for t in range(a + b):
+            cache[mine[t // P], (t % P) * row:(t % P + 1) * row] = rows[t]
+    table = i32(table)
+    starts, entry = layout(new)
+    positions = [a + t for a, b in zip(held, new) for t in range(b)]
+    q = (rnd(sum(new), H * row, seed=4) * 1.5).to(torch.bfloat16).to(DEV)
+    sink = rnd(H, seed=5).to(DEV)
+    scale = row ** -0.5
+    want = kernels.attention_rows(q, cache, i32(entry), i32(positions), table, H, scale, kv_heads=1, v_dim=R, sink=sink,
+                                  values_in_keys=True).float()
+    got = kernels.attention_latent(q, cache, i32(starts), i32(held), table, H, R, scale, sink=sink).float()
+    assert kernels.read_error_flag(DEV) == 0
+    assert (got - want).abs().max().item() < 0.02, (got - want).abs().max().item()
+    one = kernels.attention_latent(q[-1:], cache, i32([0, 1]), i32(held[2:]), table[2:], H, R, scale, n_splits=splits, sink=sink).float()
+    assert (one - want[-1:]).abs().max().item() < 0.02
+    none = kernels.attention_latent(q[-1:], cache, i32([0, 1]), i32(held[2:]), table[2:], H, R, scale, n_splits=splits).float()
+    plain_one = kernels.attention_rows(q[-1:], cache, i32([0]), i32(positions[-1:]), table[2:], H, scale, kv_heads=1, v_dim=R,
+                                       values_in_keys=True).float()
+    assert (none - plain_one).abs().max().item() < 0.02
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_a_marked_latent_row_decides_the_output_of_the_tensor_core_kernel(decode):
+    """600 rows of noise and one whose last element answers the query a hundred times better, placed at the first row, at
+    page and tile borders, and at the query's own place: the output is that row's first elements. One place later than
+    the query it is not seen."""
+    from damendaemon_b200 import kernels
+    H, R, dr, P, T = 3, 32, 16, 16, 600
+    row = R + dr
+    for marked in (0, 63, 64, 16 * 17 - 1, 16 * 17, T - 2, T - 1):
+        for at in (T - 1, marked, marked - 1):
+            if at < 0:
+                continue
+            rows = (rnd(T, row, seed=marked + 1) * 0.05).to(torch.bfloat16)
+            rows[marked, :R] = torch.arange(R) / 8.0 - 2.0
+            rows[marked, row - 1] = 6.0
+            cache = rows.view(-1).clone()
+            cache = torch.cat([cache, torch.zeros((-T % P) * row, dtype=torch.bfloat16)]).view(-1, P * row).to(DEV)
+            table = i32([list(range(cache.shape[0]))])
+            q = torch.zeros(T, H * row, dtype=torch.bfloat16)
+            q.view(T, H, row)[:, :, row - 1] = 6.0
+            q = q.to(DEV)
+            if decode:
+                out = kernels.attention_latent(q[at:at + 1], cache, i32([0, 1]), i32([at]), table, H, R, 1.0, n_splits=3)[0]
+            else:
+                out = kernels.attention_latent(q[:at + 1], cache, i32([0, at + 1]), i32([0]), table, H, R, 1.0)[at]
+            out = out.float().cpu().view(H, R)
+            if at >= marked:
+                assert (out - rows[marked, :R].float()).abs().max() < 0.02, (marked, at)
+            else:
+                assert out.abs().max() < 0.2, (marked, at)
+
+
+@pytest.mark.parametrize("n,H,I,J,tail,stride_pad", [(130, 3, 48, 40, 8, 0), (1, 25, 64, 256, 64, 0), (77, 2, 256, 130, 0, 24), (9, 5, 40, 6, 8, 8),
+                                                     (64, 1, 512, 128, 0, 0)])
+def test_per_head_products_on_the_tensor_cores(n, H, I, J, tail, stride_pad):
+    from damendaemon_b200 import kernels
+    x = rnd(n, H * (I + tail) + stride_pad, seed=1).to(torch.bfloat16).to(DEV)
+    w = (rnd(H, J, I, seed=2) / math.sqrt(I)).to(torch.bfloat16).to(DEV)
+    got = kernels.per_head_linear(x[:, :H * (I + tail)], w, I + tail, tail=tail, kernel="mma").float().view(n, H, J + tail)
+    heads = x[:, :H * (I + tail)].float().view(n, H, I + tail)
+    want = torch.einsum("nhi,hji->nhj", heads[..., :I].double(), w.double())
+    assert (got[..., :J].double() - want).abs().max().item() < 0.03
+    assert torch.equal(got[..., J:], heads[..., I:])
+    plain_kernel = kernels.per_head_linear(x[:, :H * (I + tail)], w, I + tail, tail=tail, kernel="plain").float().view(n, H, J + tail)
+    assert (got - plain_kernel).abs().max().item() < 0.03
+
+
 # ------------------------------------------------------------------ the clamped gated unit through the feed-forward part
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
