@@ -237,8 +237,7 @@ def _latent_attention_case(batch, length, dev, decode, kernel="tensor"):
         start = torch.arange(batch + 1, dtype=torch.int32, device=dev) * (1 if decode else length)
         pos0 = torch.full((batch,), context - 1 if decode else 0, dtype=torch.int32, device=dev)
         if decode:
-            tiles = -(-batch * H // 64) + batch
-            splits = max(1, min(-(-(K.sm_count(dev) * 2) // tiles), (context + 127) // 128, 32))
+            splits = K.attention_latent_splits(batch, batch, H, context, dev)
         run = lambda i: K.attention_latent(q, caches[i % copies], start, pos0, table, H, RANK, 0.1, n_splits=splits, sink=sink)
     else:
         run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, 0.1, n_splits=splits, kv_heads=1, v_dim=RANK,

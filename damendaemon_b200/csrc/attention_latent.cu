@@ -4,8 +4,8 @@
 // attention_latent_kernel: one cached row of DK bfloat16 a token is the key of EVERY head, and its first DV elements
 // are the value. So the query rows of a block are (token, head) pairs: 64 consecutive pairs of one entry (a run of
 // consecutive tokens of one request; a decoded token is a run of one, whose heads alone fill a good part of a tile),
-// against key tiles of 64 rows that are copied once for all of them (cp.async, double buffered, rows padded by 16
-// bytes so that ldmatrix is free of bank conflicts at every row length). A warp owns 16 query rows and a slice of the
+// against key tiles of 64 rows that are copied once for all of them (cp.async; two buffers, or one where that lets two
+// blocks share an SM; rows padded by 16 bytes so that ldmatrix is free of bank conflicts at every row length). A warp owns 16 query rows and a slice of the
 // value columns; with two slices (DV above 256) both warps of a row compute the same scores. Scores, softmax and the
 // weighted sums are float32; the softmax weights meet the values as two bfloat16 terms (the weight rounded, and what
 // the rounding left over), so that no weight is rounded to 8 bits. A sink joins the denominator at the end. The keys
@@ -17,7 +17,7 @@
 #include <math_constants.h>
 
 namespace {
-constexpr int BQ = 64, BKV = 64;
+constexpr int BKV = 64;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -45,21 +45,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ float bf16_low(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_high(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-// VT: pairs of 8-column value tiles a warp accumulates (VT * 16 value columns a warp).
-template <int VT>
+// VT: pairs of 8-column value tiles a warp accumulates (VT * 16 value columns a warp). RG: groups of 16 query rows a
+// block (4 for prompts; 2 for steps of single tokens with at most 32 heads, whose one token fills half a tile of 64).
+template <int VT, int RG>
 __global__ void __launch_bounds__(256)
 attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ cache,
                         const int* __restrict__ entry_start, const int* __restrict__ entry_pos0, int n_entries,
                         const int* __restrict__ block_table, int max_blocks, __nv_bfloat16* __restrict__ out,
                         int out_stride, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int DK, int DV,
                         int P, int n_pages, float scale_log2e, int n_splits, int* __restrict__ error_flag,
-                        const float* __restrict__ sink) {
+                        const float* __restrict__ sink, int n_bufs) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int BQ = RG * 16;
     const int NC = DK / 8;                    // 16-byte chunks of a row
     const int KS = DK / 16;                   // k-steps over a row
     const int RB = DK * 2 + 16;               // bytes of a padded row in shared memory
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + BQ * RB;               // [2][BKV] rows
+    uint8_t* sK = sQ + BQ * RB;               // [n_bufs][BKV] rows
     dd_launch_dependents();
     dd_grid_wait();
 
@@ -78,7 +80,7 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int* bt = block_table + (size_t)e * max_blocks;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, threads = blockDim.x;
     const int g = lane >> 2, t4 = lane & 3;
-    const int rg = warp & 3, vh = warp >> 2;                  // the warp's 16 rows, and its slice of the value columns
+    const int rg = warp % RG, vh = warp / RG;                 // the warp's 16 rows, and its slice of the value columns
 
     for (int idx = tid; idx < BQ * NC; idx += threads) {
         const int r = idx / NC, c = idx % NC;
@@ -126,10 +128,12 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     if (tile_lo < tile_hi) load_k(tile_lo * BKV, 0);
     cp_commit();
     for (int j = tile_lo; j < tile_hi; ++j) {
-        const int kb = j * BKV, buf = (j - tile_lo) & 1;
-        if (j + 1 < tile_hi) load_k(kb + BKV, buf ^ 1);
-        cp_commit();
-        cp_wait<1>();
+        const int kb = j * BKV, buf = n_bufs == 2 ? (j - tile_lo) & 1 : 0;
+        if (n_bufs == 2) {
+            if (j + 1 < tile_hi) load_k(kb + BKV, buf ^ 1);
+            cp_commit();
+            cp_wait<1>();
+        } else cp_wait<0>();
         __syncthreads();
         const uint32_t tk = smem_addr(sK + buf * BKV * RB);
         float s[8][4];
@@ -195,6 +199,8 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             a2[1] = pack_bf16(s[2 * kk][2] - bf16_low(a[1]), s[2 * kk][3] - bf16_high(a[1]));
             a2[2] = pack_bf16(s[2 * kk + 1][0] - bf16_low(a[2]), s[2 * kk + 1][1] - bf16_high(a[2]));
             a2[3] = pack_bf16(s[2 * kk + 1][2] - bf16_low(a[3]), s[2 * kk + 1][3] - bf16_high(a[3]));
+            // the rounded weights over all value columns, then the left-overs: two products into one accumulator lie
+            // a whole pass apart
 #pragma unroll
             for (int dp = 0; dp < VT; ++dp) {
                 const int col = col_base + dp * 16;
@@ -203,12 +209,24 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                     ldmatrix_x4_trans(tk + kk * 16 * RB + v_frag + col * 2, b);
                     mma_bf16(o[2 * dp], a, b[0], b[1]);
                     mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+                }
+            }
+#pragma unroll
+            for (int dp = 0; dp < VT; ++dp) {
+                const int col = col_base + dp * 16;
+                if (col < DV) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(tk + kk * 16 * RB + v_frag + col * 2, b);
                     mma_bf16(o[2 * dp], a2, b[0], b[1]);
                     mma_bf16(o[2 * dp + 1], a2, b[2], b[3]);
                 }
             }
         }
         __syncthreads();
+        if (n_bufs == 1 && j + 1 < tile_hi) {
+            load_k(kb + BKV, 0);
+            cp_commit();
+        }
     }
     cp_wait<0>();
 #pragma unroll
@@ -350,24 +368,29 @@ per_head_mma_kernel(const __nv_bfloat16* __restrict__ in, int in_stride, int in_
         }
 }
 
-template <int VT>
+template <int VT, int RG>
 int launch_latent(const void* q, int q_stride, const void* cache, const int* entry_start, const int* entry_pos0, int n_entries,
                   int n_tokens, const int* block_table, int max_blocks, void* out, int out_stride, float* part_o,
                   float* part_ml, int H, int DK, int DV, int P, int n_pages, float scale, int n_splits, int* error_flag,
                   const float* sink, cudaStream_t s) {
-    const int smem = (BQ + 2 * BKV) * (DK * 2 + 16);
+    constexpr int BQ = RG * 16;
+    // two key buffers, unless only one lets two blocks share an SM: with a warp a scheduler the tensor pipe idles most
+    // of the time (measured: 17% active), and a second block fills more of it than a block's own prefetch
+    const int half_sm = 113 * 1024;
+    const int n_bufs = (BQ + 2 * BKV) * (DK * 2 + 16) > half_sm && (BQ + BKV) * (DK * 2 + 16) <= half_sm ? 1 : 2;
+    const int smem = (BQ + n_bufs * BKV) * (DK * 2 + 16);
     static int configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_latent_kernel<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_latent_kernel<VT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return dd_fail("dd_attention_latent: shared memory refused: %s", cudaGetErrorString(e));
         configured = smem;
     }
     const int slices = dd_ceil_div(DV, VT * 16);
-    // an upper bound of the number of 64-row tiles; blocks beyond the real count return at once
+    // an upper bound of the number of tiles; blocks beyond the real count return at once
     dim3 grid(dd_ceil_div((long long)n_tokens * H, BQ) + n_entries, n_splits);
-    dd_launch(attention_latent_kernel<VT>, grid, dim3(128 * slices), (size_t)smem, s, (const __nv_bfloat16*)q, q_stride,
+    dd_launch(attention_latent_kernel<VT, RG>, grid, dim3(32 * RG * slices), (size_t)smem, s, (const __nv_bfloat16*)q, q_stride,
               (const __nv_bfloat16*)cache, entry_start, entry_pos0, n_entries, block_table, max_blocks, (__nv_bfloat16*)out,
-              out_stride, part_o, part_ml, H, DK, DV, P, n_pages, scale * 1.4426950408889634f, n_splits, error_flag, sink);
+              out_stride, part_o, part_ml, H, DK, DV, P, n_pages, scale * 1.4426950408889634f, n_splits, error_flag, sink, n_bufs);
     return dd_check_launch("dd_attention_latent");
 }
 }  // namespace
@@ -377,6 +400,9 @@ int launch_latent(const void* q, int q_stride, const void* cache, const int* ent
 DD_API int dd_attention_latent_supported(int dk, int dv, int dtype) {
     return dtype == DD_BF16 && dk > 0 && dv > 0 && dk % 16 == 0 && dv % 16 == 0 && dv <= dk && dk <= 576 && dv <= 512;
 }
+
+// The query rows of a tile: 32 where every entry is a single token of at most 32 heads, else 64.
+DD_API int dd_attention_latent_tile(int n_tokens, int n_entries, int H) { return n_tokens == n_entries && H <= 32 ? 32 : 64; }
 
 // q: [N, q_stride] rows of H * DK; cache: [n_pages, P * DK]; entries are runs of consecutive tokens of one request
 // (entry_start [E+1], entry_pos0 [E], block_table row e). out: [N, out_stride] rows of H * DV. part_o
@@ -393,11 +419,15 @@ DD_API int dd_attention_latent(const void* q, int q_stride, const void* cache, c
     if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!part_o || !part_ml))) return dd_fail("dd_attention_latent: bad splits");
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-#define DD_LATENT(VT) launch_latent<VT>(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks, \
+#define DD_LATENT(VT, RG) launch_latent<VT, RG>(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks, \
                                         out, out_stride, part_o, part_ml, H, DK, DV, P, n_pages, scale, n_splits, error_flag, sink, s)
-    if (DV <= 64) rc = DD_LATENT(4);
-    else if (DV <= 128) rc = DD_LATENT(8);
-    else rc = DD_LATENT(16);
+    if (dd_attention_latent_tile(n_tokens, n_entries, H) == 32) {
+        // single tokens: more warps with fewer value columns each (both slices of a row compute its scores)
+        if (DV <= 64) rc = DD_LATENT(4, 2);
+        else rc = DD_LATENT(8, 2);
+    } else if (DV <= 64) rc = DD_LATENT(4, 4);
+    else if (DV <= 128) rc = DD_LATENT(8, 4);
+    else rc = DD_LATENT(16, 4);
 #undef DD_LATENT
     if (rc || n_splits == 1) return rc;
     dd_launch(attention_latent_merge_kernel, dim3(dd_ceil_div((long long)n_tokens * H, 4)), dim3(128), 0, s, (const float*)part_o,

@@ -103,15 +103,30 @@ __device__ __forceinline__ void group_scales(const float* __restrict__ a, float*
                                              int width, int groups, float eps, float* partial) {
     const int gw = width / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pieces = groups >= 8 ? 1 : 8 / groups, piece = (gw + pieces - 1) / pieces;
-    const int per_row = groups * pieces, items = b ? 2 * per_row : per_row;
-    for (int it = warp; it < items; it += THREADS / 32) {
-        const int within = it % per_row, g = within / pieces, lo = (within % pieces) * piece, hi = min(gw, lo + piece);
-        const float* part = (it >= per_row ? b : a) + (size_t)g * gw;
-        float sq = 0.f;
-#pragma unroll 4
-        for (int c = lo + lane; c < hi; c += 32) sq = fmaf(part[c], part[c], sq);
-        sq = dd_warp_sum(sq);
-        if (lane == 0) partial[it] = sq;
+    const int per_row = groups * pieces;
+    // a warp sums the same piece of both rows at once, so that the loads of both are in flight together
+    for (int it = warp; it < per_row; it += THREADS / 32) {
+        const int g = it / pieces, lo = (it % pieces) * piece, hi = min(gw, lo + piece);
+        const float* pa = a + (size_t)g * gw;
+        const float* pb = b ? b + (size_t)g * gw : pa;
+        float sa = 0.f, sb = 0.f;
+        for (int c0 = lo + lane; c0 < hi; c0 += 256) {      // eight loads a row in flight; a zero past the end adds nothing
+            float va[8], vb[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) va[k] = c0 + 32 * k < hi ? pa[c0 + 32 * k] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) vb[k] = b && c0 + 32 * k < hi ? pb[c0 + 32 * k] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sa = fmaf(va[k], va[k], sa);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sb = fmaf(vb[k], vb[k], sb);
+        }
+        sa = dd_warp_sum(sa);
+        sb = dd_warp_sum(sb);
+        if (lane == 0) {
+            partial[it] = sa;
+            partial[per_row + it] = sb;
+        }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < (b ? 2 : 1) * groups; i += THREADS) {
@@ -137,6 +152,7 @@ rmsnorm_groups_kernel(const float* __restrict__ x, const int* __restrict__ row_i
     TO* o = out + (size_t)row * width;
     group_scales<THREADS>(in, r, nullptr, nullptr, width, groups, eps, partial);
     const int gw = width / groups;
+#pragma unroll 4
     for (int c = threadIdx.x; c < width; c += THREADS) o[c] = dd_from_f32<TO>(in[c] * r[c / gw] * (offset + weight[c]));
 }
 
@@ -165,6 +181,7 @@ rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ weig
         // the token before lies in this step: its normed row again, by the same arithmetic
         const float* before = in - width;
         group_scales<THREADS>(in, r_own, before, r_other, width, groups, eps, partial);
+#pragma unroll 4
         for (int c = threadIdx.x; c < width; c += THREADS) {
             const float w = offset + weight[c];
             const float n = normed_value(in[c], r_own[c / gw], w), p = normed_value(before[c], r_other[c / gw], w);

@@ -79,6 +79,7 @@ _SIGNATURES = {
         "dd_attention_prefill_sinks": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                       + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_void, _c_int],
         "dd_attention_latent_supported": [_c_int] * 3,
+        "dd_attention_latent_tile": [_c_int] * 3,
         "dd_attention_latent": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int,
                                 _c_void, _c_void] + [_c_int] * 5 + [_c_float, _c_int, _c_void, _c_void, _c_void],
         "dd_per_head_mma_supported": [_c_int] * 6,
@@ -484,6 +485,16 @@ def per_head_linear(x, w, in_head, out_head=None, tail=0, out=None, kernel=None)
 
 def attention_latent_supported(row, v_dim, dtype):
     return dtype == torch.bfloat16 and bool(library("tensor").dd_attention_latent_supported(row, v_dim, BF16))
+
+
+def attention_latent_splits(n_tokens, n_entries, n_heads, context, device):
+    """Into how many pieces a step of single tokens cuts its keys so that its tiles fill the GPU about twice (a piece is
+    at least one key tile of 64); 1 for a step with portions of prompts."""
+    if n_tokens != n_entries:
+        return 1
+    tile = int(library("tensor").dd_attention_latent_tile(n_tokens, n_entries, n_heads))
+    tiles = n_entries * -(-n_heads // tile)
+    return max(1, min(-(-2 * sm_count(device) // tiles), -(-context // 64), 32))
 
 
 def attention_latent(q, cache, entry_start, entry_pos0, block_table, n_heads, v_dim, scale, n_splits=1, sink=None, out=None):

@@ -80,9 +80,9 @@ class LatentAttention(Mixer):
         # every head's query against the cached rows: [W_uk^T q_plain | q_rotated]
         q_rows = kernels.per_head_linear(q, self.key_t, s.head_dim + s.rot_dim, tail=s.rot_dim)
         if self.runtime.attention != "rows" and kernels.attention_latent_supported(s.rank + s.rot_dim, s.rank, q_rows.dtype):
-            # tensor-core tiles of 64 (token, head) pairs; a step of single tokens cuts its keys so that the GPU fills
-            tiles = -(-ctx.n_tokens * s.n_heads // 64) + ctx.n_entries
-            splits = max(1, min(-(-2 * ctx.sm_count // tiles), -(-ctx.split_context // 128), 32)) if ctx.decode_only else 1
+            # tensor-core tiles of (token, head) pairs; a step of single tokens cuts its keys so that the GPU fills
+            splits = kernels.attention_latent_splits(ctx.n_tokens, ctx.n_entries, s.n_heads, ctx.split_context, q_rows.device) \
+                if ctx.decode_only else 1
             mixed = kernels.attention_latent(q_rows, cache.kv, ctx.entry_start, ctx.entry_pos0, table, s.n_heads, s.rank,
                                              s.scale, n_splits=splits, sink=self.sink)
         else:
