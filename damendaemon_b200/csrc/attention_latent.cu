@@ -90,21 +90,30 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             cp_async16(dst, q + (size_t)(tok0 + pr / H) * q_stride + (size_t)(pr % H) * DK + c * 8);
         } else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
-    auto load_k = [&](int kb, int buf) {
-        for (int idx = tid; idx < BKV * NC; idx += threads) {
-            const int r = idx / NC, c = idx % NC;
-            const int key = kb + r;
-            uint8_t* dst = sK + (buf * BKV + r) * RB + c * 16;
+    // The pages of a tile's keys are looked up one tile ahead, a thread a key, into shared memory: the copy loop then has
+    // no load that its copies wait for. -1: a key that no query of the tile sees, or one without a page (error bit 2).
+    __shared__ int s_page[2][BKV];
+    auto find_pages = [&](int kb, int slot) {
+        if (tid < BKV) {
+            const int key = kb + tid;
             int page = -1;
             if (key <= pos_last) {
                 const int blk = key / P;
                 page = blk < max_blocks ? bt[blk] : -1;
                 if (page < 0 || page >= n_pages) {
-                    if (c == 0) atomicOr(error_flag, 4);
+                    atomicOr(error_flag, 4);
                     page = -1;
                 }
             }
-            if (page >= 0) cp_async16(dst, cache + ((size_t)page * P + key % P) * DK + c * 8);
+            s_page[slot][tid] = page;
+        }
+    };
+    auto load_k = [&](int kb, int buf, int slot) {
+        for (int idx = tid; idx < BKV * NC; idx += threads) {
+            const int r = idx / NC, c = idx % NC;
+            uint8_t* dst = sK + (buf * BKV + r) * RB + c * 16;
+            const int page = s_page[slot][r];
+            if (page >= 0) cp_async16(dst, cache + ((size_t)page * P + (kb + r) % P) * DK + c * 8);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);   // 0 * stale NaN would spoil the sum
         }
     };
@@ -125,16 +134,20 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const uint32_t v_frag = (uint32_t)(((mi & 1) * 8 + (lane & 7)) * RB + (mi >> 1) * 16);
     const int col_base = vh * VT * 16;
 
-    if (tile_lo < tile_hi) load_k(tile_lo * BKV, 0);
+    find_pages(tile_lo * BKV, 0);
+    __syncthreads();
+    if (tile_lo < tile_hi) load_k(tile_lo * BKV, 0, 0);
     cp_commit();
+    find_pages((tile_lo + 1) * BKV, 1);
     for (int j = tile_lo; j < tile_hi; ++j) {
-        const int kb = j * BKV, buf = n_bufs == 2 ? (j - tile_lo) & 1 : 0;
-        if (n_bufs == 2) {
-            if (j + 1 < tile_hi) load_k(kb + BKV, buf ^ 1);
+        const int kb = j * BKV, buf = n_bufs == 2 ? (j - tile_lo) & 1 : 0, slot = (j - tile_lo) & 1;
+        cp_wait<0>();
+        __syncthreads();                    // tile j has landed, and the pages of tile j + 1 are known to all
+        if (n_bufs == 2 && j + 1 < tile_hi) {
+            load_k(kb + BKV, buf ^ 1, slot ^ 1);
             cp_commit();
-            cp_wait<1>();
-        } else cp_wait<0>();
-        __syncthreads();
+        }
+        find_pages(kb + 2 * BKV, slot);     // (tile j's own pages have been used)
         const uint32_t tk = smem_addr(sK + buf * BKV * RB);
         float s[8][4];
 #pragma unroll
@@ -224,7 +237,7 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         }
         __syncthreads();
         if (n_bufs == 1 && j + 1 < tile_hi) {
-            load_k(kb + BKV, 0);
+            load_k(kb + BKV, 0, slot ^ 1);
             cp_commit();
         }
     }
@@ -265,7 +278,8 @@ attention_latent_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     }
 }
 
-// One warp a (token, head): the splits' partial sums, brought to one maximum (the sink's too), added and normed.
+// One warp a (token, head): the splits' partial sums, brought to one maximum (the sink's too), added and normed. Lane s
+// holds split s's weight (at most 32 splits); a lane adds four neighbouring columns, 16 bytes a load, several in flight.
 __global__ void __launch_bounds__(128)
 attention_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                               __nv_bfloat16* __restrict__ out, int out_stride, int n_tokens, int H, int DV, int n_splits,
@@ -277,18 +291,35 @@ attention_latent_merge_kernel(const float* __restrict__ part_o, const float* __r
     if (row >= (long long)n_tokens * H) return;
     const int t = (int)(row / H), h = (int)(row % H);
     const float* ml = part_ml + (size_t)row * n_splits * 2;
-    float mx = sink ? sink[h] * 1.4426950408889634f : -CUDART_INF_F;
-    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, ml[2 * s]);
-    float total = sink ? exp2f(sink[h] * 1.4426950408889634f - mx) : 0.f;
-    for (int s = 0; s < n_splits; ++s)
-        if (ml[2 * s] != -CUDART_INF_F) total += ml[2 * s + 1] * exp2f(ml[2 * s] - mx);
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    const float m_mine = lane < n_splits ? ml[2 * lane] : -CUDART_INF_F;
+    const float l_mine = lane < n_splits ? ml[2 * lane + 1] : 0.f;
+    const float s2 = sink ? sink[h] * 1.4426950408889634f : -CUDART_INF_F;
+    float mx = fmaxf(m_mine, s2);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float w = m_mine == -CUDART_INF_F ? 0.f : exp2f(m_mine - mx);
+    float total = w * l_mine;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+    if (sink) total += exp2f(s2 - mx);
+    w *= total > 0.f ? 1.f / total : 0.f;
+    const float* po = part_o + (size_t)row * n_splits * DV;
     __nv_bfloat16* dst = out + (size_t)t * out_stride + (size_t)h * DV;
-    for (int c = lane; c < DV; c += 32) {
-        float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s)
-            if (ml[2 * s] != -CUDART_INF_F) acc += part_o[((size_t)row * n_splits + s) * DV + c] * exp2f(ml[2 * s] - mx);
-        dst[c] = __float2bfloat16(acc * inv);
+    for (int c0 = 0; c0 < DV; c0 += 128) {   // (every lane walks the loop: the weights travel by shuffles)
+        const int c = c0 + lane * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) {
+            const float ws = __shfl_sync(0xffffffffu, w, s);
+            if (ws != 0.f && c < DV) {       // (a split without visible keys has weight 0)
+                const float4 v = *reinterpret_cast<const float4*>(po + (size_t)s * DV + c);
+                acc.x = fmaf(ws, v.x, acc.x); acc.y = fmaf(ws, v.y, acc.y); acc.z = fmaf(ws, v.z, acc.z); acc.w = fmaf(ws, v.w, acc.w);
+            }
+        }
+        if (c < DV) {
+            *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(acc.x, acc.y);
+            *reinterpret_cast<uint32_t*>(dst + c + 2) = pack_bf16(acc.z, acc.w);
+        }
     }
 }
 
@@ -416,7 +447,7 @@ DD_API int dd_attention_latent(const void* q, int q_stride, const void* cache, c
         return dd_fail("dd_attention_latent: rows of %d with values of %d are not supported", DK, DV);
     if (q_stride % 8 || out_stride % 2 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 3))
         return dd_fail("dd_attention_latent: rows must be 16-byte aligned");
-    if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!part_o || !part_ml))) return dd_fail("dd_attention_latent: bad splits");
+    if (n_splits < 1 || n_splits > 32 || (n_splits > 1 && (!part_o || !part_ml))) return dd_fail("dd_attention_latent: bad splits");
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
 #define DD_LATENT(VT, RG) launch_latent<VT, RG>(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks, \
