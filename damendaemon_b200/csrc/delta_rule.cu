@@ -20,6 +20,11 @@
 namespace {
 __device__ __forceinline__ float dr_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float dr_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+template <int BYTES> __device__ __forceinline__ void dr_cp_async(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    if (BYTES == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -113,12 +118,8 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   const int* __restrict__ entry_slot, float* __restrict__ state, float* __restrict__ out,
                   int H, int G, int dk, int dv) {
     constexpr int DKP = 8 * LPC, COLS = DR_THREADS / LPC;
-    extern __shared__ __align__(16) float staged[];
-    float* sq = staged;                              // [DR_TOKENS][DKP]
-    float* sk = sq + DR_TOKENS * DKP;
-    float* sg = sk + DR_TOKENS * DKP;
-    float* sv = sg + DR_TOKENS * DKP;                // [DR_TOKENS][COLS]
-    float* sb = sv + DR_TOKENS * COLS;               // [DR_TOKENS]
+    constexpr int BUF = DR_TOKENS * (3 * DKP + COLS) + DR_TOKENS;       // floats of one buffer: q, k, decay, v, beta
+    extern __shared__ __align__(16) float staged[];                      // two buffers, filled in turn by cp.async
     dd_launch_dependents();
     const int e = blockIdx.z, h = blockIdx.y, g = h / (H / G);
     const int col0 = blockIdx.x * COLS;
@@ -133,23 +134,63 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         const float4 a = *reinterpret_cast<const float4*>(sp), b = *reinterpret_cast<const float4*>(sp + 4);
         s[0] = a.x; s[1] = a.y; s[2] = a.z; s[3] = a.w; s[4] = b.x; s[5] = b.y; s[6] = b.z; s[7] = b.w;
     }
-    dd_grid_wait();
-    for (int t0 = start; t0 < end; t0 += DR_TOKENS) {
+    // rows past dk and columns past dv are never copied into: they stay the zeros written here
+    if (dk != DKP || col0 + COLS > dv)
+        for (int i = threadIdx.x; i < 2 * BUF; i += DR_THREADS) staged[i] = 0.f;
+    // 16-byte copies where every row starts on such a boundary
+    const bool wide = dk % 4 == 0 && dv % 4 == 0 && !(((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay) & 15);
+    auto stage = [&](int t0, int buf) {
         const int n = min(DR_TOKENS, end - t0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < n * DKP; i += DR_THREADS) {
-            const int tt = i / DKP, r = i % DKP;
-            const bool in = r < dk;
-            sq[i] = in ? q[(size_t)(t0 + tt) * G * dk + (size_t)g * dk + r] : 0.f;
-            sk[i] = in ? k[(size_t)(t0 + tt) * G * dk + (size_t)g * dk + r] : 0.f;
-            sg[i] = in ? decay[(size_t)(t0 + tt) * H * dk + (size_t)h * dk + r] : 0.f;
+        float* bq = staged + buf * BUF;
+        float* bk = bq + DR_TOKENS * DKP;
+        float* bg = bk + DR_TOKENS * DKP;
+        float* bv = bg + DR_TOKENS * DKP;
+        float* bb = bv + DR_TOKENS * COLS;
+        if (wide) {
+            for (int i = threadIdx.x; i < n * (DKP / 4); i += DR_THREADS) {
+                const int tt = i / (DKP / 4), r = (i % (DKP / 4)) * 4;
+                if (r < dk) {
+                    dr_cp_async<16>(bq + tt * DKP + r, q + (size_t)(t0 + tt) * G * dk + (size_t)g * dk + r);
+                    dr_cp_async<16>(bk + tt * DKP + r, k + (size_t)(t0 + tt) * G * dk + (size_t)g * dk + r);
+                    dr_cp_async<16>(bg + tt * DKP + r, decay + (size_t)(t0 + tt) * H * dk + (size_t)h * dk + r);
+                }
+            }
+            for (int i = threadIdx.x; i < n * (COLS / 4); i += DR_THREADS) {
+                const int tt = i / (COLS / 4), c = (i % (COLS / 4)) * 4;
+                if (col0 + c < dv) dr_cp_async<16>(bv + tt * COLS + c, v + (size_t)(t0 + tt) * H * dv + (size_t)h * dv + col0 + c);
+            }
+        } else {
+            for (int i = threadIdx.x; i < n * DKP; i += DR_THREADS) {
+                const int tt = i / DKP, r = i % DKP;
+                if (r < dk) {
+                    dr_cp_async<4>(bq + i, q + (size_t)(t0 + tt) * G * dk + (size_t)g * dk + r);
+                    dr_cp_async<4>(bk + i, k + (size_t)(t0 + tt) * G * dk + (size_t)g * dk + r);
+                    dr_cp_async<4>(bg + i, decay + (size_t)(t0 + tt) * H * dk + (size_t)h * dk + r);
+                }
+            }
+            for (int i = threadIdx.x; i < n * COLS; i += DR_THREADS) {
+                const int tt = i / COLS, c = i % COLS;
+                if (col0 + c < dv) dr_cp_async<4>(bv + i, v + (size_t)(t0 + tt) * H * dv + (size_t)h * dv + col0 + c);
+            }
         }
-        for (int i = threadIdx.x; i < n * COLS; i += DR_THREADS) {
-            const int tt = i / COLS, c = i % COLS;
-            sv[i] = col0 + c < dv ? v[(size_t)(t0 + tt) * H * dv + (size_t)h * dv + col0 + c] : 0.f;
-        }
-        if (threadIdx.x < n) sb[threadIdx.x] = beta[(size_t)(t0 + threadIdx.x) * H + h];
+        if (threadIdx.x < n) dr_cp_async<4>(bb + threadIdx.x, beta + (size_t)(t0 + threadIdx.x) * H + h);
+    };
+    dd_grid_wait();
+    __syncthreads();                                    // the zeros are written before any copy lands
+    if (start < end) stage(start, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    int buf = 0;
+    for (int t0 = start; t0 < end; t0 += DR_TOKENS, buf ^= 1) {
+        const int n = min(DR_TOKENS, end - t0);
+        if (t0 + DR_TOKENS < end) stage(t0 + DR_TOKENS, buf ^ 1);      // (that buffer's tokens were read before the last barrier)
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
+        const float* sq = staged + buf * BUF;
+        const float* sk = sq + DR_TOKENS * DKP;
+        const float* sg = sk + DR_TOKENS * DKP;
+        const float* sv = sg + DR_TOKENS * DKP;
+        const float* sb = sv + DR_TOKENS * COLS;
         for (int tt = 0; tt < n; ++tt) {
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DKP + sub * 8);
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DKP + sub * 8);
@@ -177,7 +218,9 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             for (int o = LPC / 2; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
             if (live && sub == 0) out[(size_t)(t0 + tt) * H * dv + (size_t)h * dv + col] = read;
         }
+        __syncthreads();                                // all have read this buffer before the copies after next fill it
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (live) {
         *reinterpret_cast<float4*>(sp) = make_float4(s[0], s[1], s[2], s[3]);
         *reinterpret_cast<float4*>(sp + 4) = make_float4(s[4], s[5], s[6], s[7]);
@@ -269,7 +312,7 @@ DD_API int dd_delta_rule(const float* q, const float* k, const float* v, const f
     const int lpc = lanes_per_column(dk);
     const int cols = DR_THREADS / lpc;
     const dim3 grid(dd_ceil_div(dv, cols), H, n_entries);
-    const size_t smem = (size_t)(DR_TOKENS * (3 * 8 * lpc + cols + 1)) * sizeof(float);
+    const size_t smem = (size_t)2 * (DR_TOKENS * (3 * 8 * lpc + cols + 1)) * sizeof(float);
 #define DD_RULE(L)                                                                                                      \
     do {                                                                                                                \
         if (smem > 48 * 1024)                                                                                           \
