@@ -191,32 +191,47 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         const float* sg = sk + DR_TOKENS * DKP;
         const float* sv = sg + DR_TOKENS * DKP;
         const float* sb = sv + DR_TOKENS * COLS;
-        for (int tt = 0; tt < n; ++tt) {
-            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DKP + sub * 8);
-            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DKP + sub * 8);
-            const float4* g4 = reinterpret_cast<const float4*>(sg + tt * DKP + sub * 8);
-            const float4 ka = k4[0], kb = k4[1], ga = g4[0], gb = g4[1], qa = q4[0], qb = q4[1];
-            const float kk[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
-            const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-            const float qq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-            float dot = 0.f;
+        // Four tokens at a time: the state goes through them one after the other (a token's write needs its own
+        // exchanged dot product), but their read-outs' exchanges wait until all four are there and then run level by
+        // level side by side, so that only the first dot product's exchanges lie on the chain from token to token.
+        for (int tt0 = 0; tt0 < n; tt0 += 4) {
+            float read[4];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                s[r] = __fmul_rn(s[r], gg[r]);
-                dot = __fmaf_rn(s[r], kk[r], dot);
+            for (int j = 0; j < 4; ++j) {
+                read[j] = 0.f;
+                const int tt = tt0 + j;
+                if (tt < n) {
+                    const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DKP + sub * 8);
+                    const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DKP + sub * 8);
+                    const float4* g4 = reinterpret_cast<const float4*>(sg + tt * DKP + sub * 8);
+                    const float4 ka = k4[0], kb = k4[1], ga = g4[0], gb = g4[1], qa = q4[0], qb = q4[1];
+                    const float kk[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+                    const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+                    const float qq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                    float dot = 0.f;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        s[r] = __fmul_rn(s[r], gg[r]);
+                        dot = __fmaf_rn(s[r], kk[r], dot);
+                    }
+#pragma unroll
+                    for (int o = LPC / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    const float u = __fmul_rn(sb[tt], __fsub_rn(sv[tt * COLS + my_col], dot));
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        s[r] = __fmaf_rn(kk[r], u, s[r]);
+                        read[j] = __fmaf_rn(s[r], qq[r], read[j]);
+                    }
+                }
             }
 #pragma unroll
-            for (int o = LPC / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = __fmul_rn(sb[tt], __fsub_rn(sv[tt * COLS + my_col], dot));
-            float read = 0.f;
+            for (int o = LPC / 2; o > 0; o >>= 1) {
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                s[r] = __fmaf_rn(kk[r], u, s[r]);
-                read = __fmaf_rn(s[r], qq[r], read);
+                for (int j = 0; j < 4; ++j) read[j] += __shfl_xor_sync(0xffffffffu, read[j], o);
             }
 #pragma unroll
-            for (int o = LPC / 2; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
-            if (live && sub == 0) out[(size_t)(t0 + tt) * H * dv + (size_t)h * dv + col] = read;
+            for (int j = 0; j < 4; ++j)
+                if (tt0 + j < n && live && sub == 0) out[(size_t)(t0 + tt0 + j) * H * dv + (size_t)h * dv + col] = read[j];
         }
         __syncthreads();                                // all have read this buffer before the copies after next fill it
     }
