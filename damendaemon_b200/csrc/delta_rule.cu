@@ -4,7 +4,8 @@
 //     S <- g[:, None] * S;   u = beta * (v - S^T k);   S <- S + k u^T;   o = S^T q
 // so the read-out sees the token's own write. Column j of o depends on column j of S only, so a thread block owns
 // (entry, head, a run of columns); a column's rows are dealt out over LPC neighbouring lanes, eight rows each in
-// registers, and the two dot products of a token are a few exchanges between those lanes. The state is stored column
+// registers, and the two dot products of a token are a few exchanges between those lanes (the read-outs' exchanges of
+// four tokens run side by side). Tokens are staged 16 at a time by cp.async into two buffers in turn. The state is stored column
 // by column ([slots, heads, dv, 8 * LPC], rows past dk stay zero), a thread's rows as two 16-byte pieces. A portion of
 // a prompt and a single token run the same instructions in the same order, so a prompt cut anywhere gives the same
 // bits.

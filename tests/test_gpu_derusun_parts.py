@@ -484,7 +484,7 @@ def test_a_far_latent_row_among_hundreds_is_found():
         assert (got - want).abs().max() < 2e-2, marked
 
 
-@pytest.mark.parametrize("H,R,dr,splits", [(5, 48, 16, 1), (25, 256, 64, 1), (3, 320, 32, 3), (7, 448, 64, 2), (2, 16, 16, 4), (16, 80, 48, 1)])
+@pytest.mark.parametrize("H,R,dr,splits", [(5, 48, 16, 1), (25, 256, 64, 1), (3, 320, 32, 3), (7, 448, 64, 2), (2, 16, 16, 4), (16, 80, 48, 1), (40, 64, 16, 2), (33, 144, 32, 3)])
 def test_tensor_core_attention_over_latent_rows_against_the_general_kernel(H, R, dr, splits):
     """Three requests side by side on shuffled pages: a portion that starts inside a page behind 70 cached rows, a prompt
     from its start, and a single token behind 200 rows; then the same single token with its keys cut into splits."""
