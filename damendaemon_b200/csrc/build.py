@@ -1,7 +1,7 @@
 """Compile the CUDA sources of this folder for sm_100a into shared libraries, on first use.
 
 Two libraries: ``core`` (plain CUDA-core kernels of both engine dtypes: embedding,
-LayerNorm, RMS norm (plain, in groups, blended with the token before), rotary positions, per-head norm, retention, the gated delta rule, latent rows and per-head products, weighted sums of streams, float32 GEMM, cache writes, general attention, expert routing, sampling) and ``tensor``
+LayerNorm, RMS norm (plain, in groups, blended with the token before), rotary positions, per-head norm, retention, the gated delta rule, latent rows and per-head products, weighted sums of streams, the token-pair embedding, the tanh norm and other row operations, the state-space scan, the gated linear recurrence, float32 GEMM, cache writes, general attention, expert routing, sampling) and ``tensor``
 (tcgen05/TMA GEMM, tensor-core attention, also over latent rows, and per-head products, bfloat16 only). A float32 engine needs
 only ``core``; what is compiled at the first call is what the model needs.
 
@@ -30,7 +30,8 @@ HERE = Path(__file__).resolve().parent
 
 LIBRARIES = {
     "core": ["errors.cu", "embed.cu", "layernorm.cu", "rmsnorm.cu", "rotary.cu", "head_norm.cu", "retention.cu", "gemm_simt.cu", "kv_store.cu",
-             "attention_rows.cu", "moe.cu", "sampling.cu", "depth_mix.cu", "delta_rule.cu", "latent.cu"],
+             "attention_rows.cu", "moe.cu", "sampling.cu", "depth_mix.cu", "delta_rule.cu", "latent.cu", "embed_pairs.cu", "stream_ops.cu",
+             "state_space.cu", "linear_recurrence.cu"],
     "tensor": ["errors.cu", "gemm_tcgen05.cu", "gemm_grouped_tcgen05.cu", "attention_decode.cu", "attention_decode_pages.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu", "attention_latent.cu",
                "wait_probe.cu"],
 }

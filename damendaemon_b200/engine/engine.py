@@ -99,6 +99,7 @@ class Engine:
         for i, e in enumerate(self.spec.run_order):
             if e.cache_of is not None:           # another stop's pages, but the named states of its own site
                 self._caches[i].named = self.cache.named_state.get(i, {})
+        self._caches.append(self.cache.layer_view(len(self.spec.run_order)))     # the embedding's own site
         self.check_device_errors = check_device_errors
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_graph = use_graph and self.model.graph_safe

@@ -64,6 +64,22 @@ _SIGNATURES = {
         "dd_attention_rows_sinks": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
                                    + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int,
                                       _c_int, _c_float, _c_void, _c_int],
+        "dd_embed_pairs": [_c_void] * 9 + [_c_int] * 4 + [ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_void, _c_void],
+        "dd_tanh_norm": [_c_void] * 6 + [_c_int, _c_int, _c_int, _c_void],
+        "dd_add_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
+        "dd_norm_pair_add": [_c_void] * 5 + [_c_float, _c_float, _c_int, _c_int, _c_void],
+        "dd_wide_norm_rotary": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_float] + [_c_int] * 7 + [_c_void],
+        "dd_sigmoid_gate": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+        "dd_tanh_cap": [_c_void, ctypes.c_longlong, _c_float, _c_void],
+        "dd_state_space_rows": [_c_int],
+        "dd_conv_channels": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
+                             _c_int, _c_int, _c_int, _c_int, _c_void],
+        "dd_state_space_scan": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void]
+                               + [_c_int] * 5 + [_c_void],
+        "dd_gated_group_norm": [_c_void, _c_void, _c_int, _c_void, _c_float, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+        "dd_recurrence_gates": [_c_void] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
+        "dd_linear_scan": [_c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_int,
+                           _c_int, _c_void],
         "dd_sample": [_c_void, _c_int, _c_int, _c_int] + [_c_void] * 6,
         "dd_adjust_logits": [_c_void, _c_int, _c_int] + [_c_void] * 8 + [_c_int, _c_void],
     },
@@ -275,6 +291,204 @@ def embed(ids, positions, token_table, position_table=None, out=None, scale=1.0)
           _ptr(token_table, "token table"), _ptr(position_table, "position table"), _ptr(out, "out", torch.float32),
           n, width, token_table.shape[0], 0 if position_table is None else position_table.shape[0],
           _dt(token_table.dtype), float(scale), _ptr(error_flag(ids.device)), _stream())
+    return out
+
+
+def embed_pairs(ids, positions, token_entry, entry_start, entry_slot, token_table, pair_table, last_id, mul_prev, mul_cur, out=None):
+    """x[t] = token_table[ids[t]] + pair_table[row(t)], float32; row(t) = (id before * mul_prev + ids[t] * mul_cur) mod buckets
+    with buckets = rows of pair_table - 1, and the table's last row for a token at position 0. ``last_id``: int32 [slots], the
+    id before an entry's first token (read), replaced by the entry's last id."""
+    n, width = ids.numel(), token_table.shape[1]
+    if pair_table.dtype != token_table.dtype or pair_table.shape[1] != width or pair_table.shape[0] < 2 or \
+            not pair_table.is_contiguous() or not token_table.is_contiguous():
+        raise KernelError("embed_pairs: the pair table must have the token table's dtype and width")
+    if last_id.dtype != torch.int32 or last_id.dim() != 1 or not last_id.is_contiguous():
+        raise KernelError("embed_pairs: the state must be int32 [slots]")
+    if out is None:
+        out = torch.empty((n, width), dtype=torch.float32, device=ids.device)
+    _call(library("core"), "dd_embed_pairs", _ptr(ids, "ids", torch.int32), _ptr(positions, "positions", torch.int32),
+          _ptr(token_entry, "token_entry", torch.int32), _ptr(entry_start, "entry_start", torch.int32),
+          _ptr(entry_slot, "entry_slot", torch.int32), _ptr(token_table, "token table"), _ptr(pair_table, "pair table"),
+          _ptr(last_id), _ptr(out, "out", torch.float32), n, width, token_table.shape[0], pair_table.shape[0] - 1, int(mul_prev),
+          int(mul_cur), _dt(token_table.dtype), _ptr(error_flag(ids.device)), _stream())
+    return out
+
+
+def tanh_norm(x, alpha, weight, bias, out_dtype, row_index=None, out=None):
+    """tanh(alpha * x) * weight + bias over float32 rows (alpha: float32, one number on the device), float32 inside."""
+    _rows(x, "x")
+    rows = x.shape[0] if row_index is None else row_index.numel()
+    width = x.shape[1]
+    if not x.is_contiguous():
+        raise KernelError("tanh_norm input must be contiguous")
+    for v, name, size in ((alpha, "alpha", 1), (weight, "weight", width), (bias, "bias", width)):
+        if v.numel() != size or v.dtype != torch.float32 or not v.is_contiguous():
+            raise KernelError(f"tanh_norm: {name} must be float32 with {size} element(s)")
+    if out is None:
+        out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    _call(library("core"), "dd_tanh_norm", _ptr(x, "x", torch.float32), _ptr(row_index, "row_index", torch.int32), _ptr(alpha),
+          _ptr(weight), _ptr(bias), _ptr(out, "out", out_dtype), rows, width, _dt(out_dtype), _stream())
+    return out
+
+
+def add_rows(x, other=None, vec=None):
+    """x += other + vec in place: x float32 [N, width] contiguous, other the same shape or None, vec float32 [width] or None."""
+    _rows(x, "x")
+    if x.dtype != torch.float32 or not x.is_contiguous() or \
+            (other is not None and (other.shape != x.shape or other.dtype != torch.float32 or not other.is_contiguous())) or \
+            (vec is not None and (vec.numel() != x.shape[1] or vec.dtype != torch.float32 or not vec.is_contiguous())):
+        raise KernelError("add_rows: float32 rows of one shape and a float32 vector of their width wanted")
+    _call(library("core"), "dd_add_rows", _ptr(x), _ptr(other), _ptr(vec), x.shape[0], x.shape[1], _stream())
+    return x
+
+
+def norm_pair_add(x, left, right, left_weight, right_weight, eps, factor=0.5):
+    """x += factor * (left / rms(left) * left_weight + right / rms(right) * right_weight), all float32 [N, width]."""
+    for t in (x, left, right):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.shape != x.shape or t.dim() != 2:
+            raise KernelError("norm_pair_add: three contiguous float32 tensors of one shape wanted")
+    for w in (left_weight, right_weight):
+        if w.numel() != x.shape[1] or w.dtype != torch.float32 or not w.is_contiguous():
+            raise KernelError("norm_pair_add: a weight must be float32 [width]")
+    _call(library("core"), "dd_norm_pair_add", _ptr(x), _ptr(left), _ptr(right), _ptr(left_weight), _ptr(right_weight), float(eps),
+          float(factor), x.shape[0], x.shape[1], _stream())
+    return x
+
+
+def wide_norm_rotary(q, k, positions, q_weight, k_weight, eps, q_heads, k_heads, head_dim, freqs=None, interleaved=True):
+    """In place: q (and k, a row view of the same buffer, or None with k_heads 0) becomes x / sqrt(mean(x^2) + eps) * weight
+    with the mean over the WHOLE projection (all heads at once) and a weight per element (float32 [heads * head_dim]; None:
+    that kind is not normed); then the first 2 * len(freqs) dimensions of every head are rotated by position * freqs as in
+    ``rotary``. All float32 inside."""
+    if k is not None and (q.stride(0) != k.stride(0) or k.stride(1) != 1 or q.dtype != k.dtype or k.shape[1] != k_heads * head_dim):
+        raise KernelError("wide_norm_rotary: q and k must be row views of one buffer")
+    if q.stride(1) != 1 or q.shape[1] != q_heads * head_dim or (k is None) != (k_heads == 0):
+        raise KernelError("wide_norm_rotary: shapes do not fit the heads")
+    for w, heads in ((q_weight, q_heads), (k_weight, k_heads)):
+        if w is not None and (w.numel() != heads * head_dim or w.dtype != torch.float32 or not w.is_contiguous()):
+            raise KernelError("wide_norm_rotary: a weight must be float32 [heads * head_dim]")
+    n_pairs = 0 if freqs is None else freqs.numel()
+    _call(library("core"), "dd_wide_norm_rotary", _ptr(q, "q"), _ptr(k, "k"), q.stride(0), _ptr(positions, "positions", torch.int32),
+          _ptr(freqs, "freqs", torch.float32), _ptr(q_weight, "q_weight"), _ptr(k_weight, "k_weight"), float(eps), q.shape[0],
+          q_heads, k_heads, head_dim, n_pairs, 1 if interleaved else 0, _dt(q.dtype), _stream())
+    return q, k
+
+
+def sigmoid_gate(x, gate):
+    """x *= sigmoid(gate) in place, element by element (float32 inside); x and gate row views of one shape and dtype."""
+    if x.shape != gate.shape or x.dim() != 2 or x.stride(1) != 1 or gate.stride(1) != 1 or x.dtype != gate.dtype:
+        raise KernelError("sigmoid_gate: two row views of one shape and dtype wanted")
+    _call(library("core"), "dd_sigmoid_gate", _ptr(x, "x"), x.stride(0), _ptr(gate, "gate"), gate.stride(0), x.shape[0], x.shape[1],
+          _dt(x.dtype), _stream())
+    return x
+
+
+def tanh_cap(x, cap):
+    """x = cap * tanh(x / cap) in place; x float32 contiguous."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("tanh_cap: contiguous float32 wanted")
+    _call(library("core"), "dd_tanh_cap", _ptr(x), x.numel(), float(cap), _stream())
+    return x
+
+
+def conv_channels(x, taps, bias, conv_state, token_entry, entry_start, entry_slot, activation=None, out=None):
+    """A short causal convolution over time per channel: out[t, c] = act(bias[c] + sum_j taps[c, j] * x[t - (n - 1 - j), c]),
+    float32 [N, channels]. x: a row view [N, channels]; taps float32 [channels, n]; bias float32 [channels] or None; the n - 1
+    inputs before an entry's first token come from conv_state float32 [slots, n - 1, channels] (``conv_state_update`` leaves
+    them there afterwards). activation: None or 'silu'."""
+    n, channels = x.shape
+    n_taps = taps.shape[1]
+    if x.stride(1) != 1 or taps.shape[0] != channels or taps.dtype != torch.float32 or not taps.is_contiguous() or \
+            conv_state.dtype != torch.float32 or not conv_state.is_contiguous() or tuple(conv_state.shape[1:]) != (n_taps - 1, channels) or \
+            (bias is not None and (bias.numel() != channels or bias.dtype != torch.float32 or not bias.is_contiguous())):
+        raise KernelError("conv_channels: shapes do not fit")
+    if out is None:
+        out = torch.empty((n, channels), dtype=torch.float32, device=x.device)
+    _call(library("core"), "dd_conv_channels", _ptr(x, "x"), x.stride(0), _ptr(taps), _ptr(bias), n_taps, _ptr(conv_state),
+          _ptr(token_entry, "token_entry", torch.int32), _ptr(entry_start, "entry_start", torch.int32),
+          _ptr(entry_slot, "entry_slot", torch.int32), _ptr(out), out.stride(0), n, channels, {None: 0, "silu": 1}[activation],
+          _dt(x.dtype), _stream())
+    return out
+
+
+def state_space_state_shape(heads, state, value_dim):
+    """Shape of one request's state-space state (float32): per head the columns of S one after the other, each padded to
+    what the lanes of a column hold."""
+    if not 0 < state <= 256 or value_dim <= 0:
+        raise KernelError(f"state space: a state of {state} by {value_dim} is not supported (at most 256 rows)")
+    lanes = 1
+    while lanes * 8 < state:
+        lanes *= 2
+    return (int(heads), int(value_dim), 8 * lanes)          # what dd_state_space_rows answers
+
+
+def state_space_scan(xbc, dt, dt_bias, a_log, skip, entry_start, entry_slot, state, heads, groups, n_state, value_dim, out=None):
+    """The state-space recurrence of a step: per entry and head h, from the state in row entry_slot[e] of ``state`` (float32
+    [slots, *state_space_state_shape(...)], read and written), token by token: step = softplus(dt + dt_bias[h]);
+    S = exp(-exp(a_log[h]) * step) * S + step * B x^T; y = S^T C + skip[h] * x. xbc: float32 [N, heads * value_dim + 2 * groups *
+    n_state] rows [x | B | C]; dt: a row view [N, heads]. Returns y float32 [N, heads * value_dim]."""
+    n = xbc.shape[0]
+    inner = heads * value_dim
+    if xbc.dtype != torch.float32 or xbc.stride(1) != 1 or xbc.shape[1] != inner + 2 * groups * n_state or dt.shape != (n, heads) or \
+            dt.stride(1) != 1 or state.dtype != torch.float32 or not state.is_contiguous() or \
+            tuple(state.shape[1:]) != state_space_state_shape(heads, n_state, value_dim):
+        raise KernelError("state_space_scan: shapes do not fit the state")
+    for v in (dt_bias, a_log, skip):
+        if v.numel() != heads or v.dtype != torch.float32 or not v.is_contiguous():
+            raise KernelError("state_space_scan: the per-head parameters must be float32 [heads]")
+    if out is None:
+        out = torch.empty((n, inner), dtype=torch.float32, device=xbc.device)
+    _call(library("core"), "dd_state_space_scan", _ptr(xbc), xbc.stride(0), _ptr(dt, "dt"), dt.stride(0), _ptr(dt_bias), _ptr(a_log),
+          _ptr(skip), _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_slot, "entry_slot", torch.int32), entry_slot.numel(),
+          _ptr(state), _ptr(out), heads, groups, n_state, value_dim, _dt(dt.dtype), _stream())
+    return out
+
+
+def gated_group_norm(y, z, weight, groups, eps, out_dtype, out=None):
+    """out = (y * silu(z)) in ``groups`` equal stretches, each divided by its root mean square (eps inside the root), times
+    weight. y float32 [N, inner] contiguous; z a row view [N, inner] in out_dtype; weight float32 [inner]."""
+    n, inner = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or z.shape != y.shape or z.stride(1) != 1 or z.dtype != out_dtype or \
+            weight.numel() != inner or weight.dtype != torch.float32 or not weight.is_contiguous() or inner % groups:
+        raise KernelError("gated_group_norm: shapes do not fit")
+    if out is None:
+        out = torch.empty((n, inner), dtype=out_dtype, device=y.device)
+    _call(library("core"), "dd_gated_group_norm", _ptr(y), _ptr(z, "z"), z.stride(0), _ptr(weight), float(eps), _ptr(out), out.stride(0),
+          n, int(groups), inner, _dt(out_dtype), _stream())
+    return out
+
+
+def recurrence_gates(u, wa, ba, wi, bi, lam, gain):
+    """The gates of a gated linear recurrence, float32: with the channels of u [N, width] in ``blocks`` equal parts (wa, wi:
+    float32 [blocks, part, part], [out, in]; ba, bi, lam: float32 [width]), r = sigmoid(wa u + ba), i = sigmoid(wi u + bi),
+    a = exp(-gain * r * softplus(lam)). Returns (1 - a, sqrt(1 - a^2) * i * u), both float32 [N, width]: the decay travels as
+    its distance from one, which float32 holds far more exactly for a slow channel than the decay itself."""
+    n, width = u.shape
+    blocks = wa.shape[0]
+    ok = all(t.dtype == torch.float32 and t.is_contiguous() for t in (u, wa, ba, wi, bi, lam))
+    if not ok or width % blocks or tuple(wa.shape) != (blocks, width // blocks, width // blocks) or wi.shape != wa.shape or \
+            any(v.numel() != width for v in (ba, bi, lam)):
+        raise KernelError("recurrence_gates: shapes do not fit")
+    a = torch.empty_like(u)
+    drive = torch.empty_like(u)
+    _call(library("core"), "dd_recurrence_gates", _ptr(u), _ptr(wa), _ptr(ba), _ptr(wi), _ptr(bi), _ptr(lam), float(gain), _ptr(a),
+          _ptr(drive), n, width, blocks, _stream())
+    return a, drive
+
+
+def linear_scan(a, drive, y, entry_start, entry_slot, state, activation=None, out=None):
+    """S = S - a[t] * S + drive[t] (a holds 1 - decay, as ``recurrence_gates`` leaves it) per channel and entry, from row entry_slot[e] of ``state`` (float32 [slots, width], read and
+    written), token by token; out[t] = S * act(y[t]) rounded once to y's dtype. activation: None or 'gelu_tanh'."""
+    n, width = a.shape
+    if a.dtype != torch.float32 or drive.dtype != torch.float32 or not a.is_contiguous() or not drive.is_contiguous() or \
+            drive.shape != a.shape or y.shape != a.shape or y.stride(1) != 1 or state.dtype != torch.float32 or \
+            not state.is_contiguous() or tuple(state.shape[1:]) != (width,):
+        raise KernelError("linear_scan: shapes do not fit the state")
+    if out is None:
+        out = torch.empty((n, width), dtype=y.dtype, device=a.device)
+    _call(library("core"), "dd_linear_scan", _ptr(a), _ptr(drive), _ptr(y, "y"), y.stride(0),
+          _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_slot, "entry_slot", torch.int32), entry_slot.numel(), _ptr(state),
+          _ptr(out), out.stride(0), width, {None: 0, "gelu_tanh": 1}[activation], _dt(y.dtype), _stream())
     return out
 
 

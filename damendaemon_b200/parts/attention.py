@@ -11,7 +11,10 @@ that rotation (one kernel does both); no keys and values of its own (the mixer t
 projects queries only and reads the cache of another stop of the run order through its own
 mask); first keys that stay visible behind the window, capped scores and a sink in the softmax (a learned number per
 head in the denominator); values blended with those an earlier mixer computed for the same tokens (one learned weight,
-the blended values are what is cached). The kernels read keys and values from the cache pages only, so
+the blended values are what is cached); values that are the keys as projected (no value projection: the key projection's
+rows are joined to the fused product a second time, so the values are the unnormed, unrotated keys bit for bit); a norm of
+queries and keys over the whole projection instead of per head; a gate per element of the attended output; a unit term in
+the softmax's denominator. The kernels read keys and values from the cache pages only, so
 a portion of a prompt sees earlier portions exactly as a decoded token sees its context.
 """
 from __future__ import annotations
@@ -39,6 +42,10 @@ def _projection(spec):
         if isinstance(names, str) or len(names) != 1:
             raise ValueError("a mixer without keys and values of its own names its query projection alone")
         names = tuple(names)
+    if spec.values_are_keys:
+        if isinstance(names, str) or len(names) != 2 or not spec.own_keys_values:
+            raise ValueError("a mixer whose values are its keys names its query and key projections (and no third)")
+        names = (names[0], names[1], names[1])        # the key projection's rows a second time: the values
     if spec.gate_weight:
         if isinstance(names, str):
             raise ValueError("a gate's rows are joined to separate query, key and value projections")
@@ -78,6 +85,15 @@ class Attention(Mixer):
             raise ValueError("a gated attention with projection biases is not supported")
         self.rotary = None if spec.rotary is None else lookup(POSITIONS, spec.rotary, "position encoding")(spec.rotary, weights, runtime)
         self.sink = weights[spec.sink] if spec.sink else None
+        if spec.unit_sink:
+            if spec.sink:
+                raise ValueError("a unit term in the softmax's denominator and a learned sink do not go together")
+            self.sink = torch.zeros(spec.n_heads, dtype=torch.float32, device=runtime.device)      # exp(0) = 1
+        if spec.values_are_keys and self.value_dim != spec.head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if spec.gate_per_element and not spec.gate_weight:
+            raise ValueError("a gate per element needs the gate's projection")
+        self.gate_width = 0 if not spec.gate_weight else (spec.n_heads * self.value_dim if spec.gate_per_element else spec.n_heads)
         self.value_mix = weights[spec.value_mix] if spec.value_mix else None
         if (spec.value_mix or spec.value_mix_source) and not spec.own_keys_values:
             raise ValueError("values are blended only by a mixer with values of its own")
@@ -102,7 +118,7 @@ class Attention(Mixer):
         if not spec.own_keys_values:
             kv = v = 0
         attended = spec.n_heads * (spec.value_dim or spec.head_dim)
-        gate = spec.n_heads if spec.gate_weight else 0
+        gate = 0 if not spec.gate_weight else (attended if spec.gate_per_element else spec.n_heads)
         total = q + kv + v + gate
         io = spec.stored_in_out
         matrix = lambda n: (spec.width, n) if io else (n, spec.width)
@@ -117,9 +133,9 @@ class Attention(Mixer):
             decls.append(TensorDecl(_joined(spec.qkv_bias), (total,), "vector", False, pieces))
         if spec.out_bias:
             decls.append(TensorDecl(spec.out_bias, (spec.width,), "vector"))
-        for name in (spec.query_norm, spec.key_norm):
+        for name, heads in ((spec.query_norm, spec.n_heads), (spec.key_norm, spec.n_kv_heads)):
             if name:
-                decls.append(TensorDecl(name, (spec.head_dim,), "vector"))
+                decls.append(TensorDecl(name, (heads * spec.head_dim if spec.norm_whole_projection else spec.head_dim,), "vector"))
         if spec.sink:
             decls.append(TensorDecl(spec.sink, (spec.n_heads,), "vector"))
         if spec.value_mix:
@@ -146,9 +162,18 @@ class Attention(Mixer):
             v = qkv[:, self.q_width + self.kv_width:self.q_width + self.kv_width + self.v_width]
         elif cache.writable:
             raise ValueError("a mixer without keys and values of its own must read another stop's cache (RunEntry.cache_of)")
-        gate = qkv[:, self.q_width + self.kv_width + self.v_width:][:, :s.n_heads] if s.gate_weight else None
+        gate = qkv[:, self.q_width + self.kv_width + self.v_width:][:, :self.gate_width] if s.gate_weight else None
         q, k = position.on_query_key(q, k, ctx)
-        if self.query_norm is not None or self.key_norm is not None or (k is None and self.rotary is not None):
+        if s.norm_whole_projection:
+            # the norm over all heads at once and the rotation, one pass (values that are the keys were projected a
+            # second time and stay as they are)
+            if self.rotary is not None and self.rotary.magnitude != 1.0:
+                raise ValueError("a norm over the whole projection takes plain rotary frequencies (no scaled cosines)")
+            kernels.wide_norm_rotary(q, k, ctx.positions, self.query_norm, self.key_norm, s.head_norm_eps, s.n_heads,
+                                     s.n_kv_heads if k is not None else 0, s.head_dim,
+                                     freqs=None if self.rotary is None else self.rotary.freqs,
+                                     interleaved=True if self.rotary is None else self.rotary.spec.interleaved)
+        elif self.query_norm is not None or self.key_norm is not None or (k is None and self.rotary is not None):
             # the heads' norm and the rotation in one pass over the projection's output (the normed value is rotated as
             # float32); a rotation that also scales cosine and sine follows as a pass of its own
             fused = self.rotary is not None and self.rotary.magnitude == 1.0
@@ -169,6 +194,8 @@ class Attention(Mixer):
             if first is None or first.shape != v.shape:
                 raise ValueError("values are blended with those of an earlier mixer of the same step and shape; none was left")
             kernels.blend_rows(v, first, self.value_mix)
-        attended = ctx.attend(q, k, v, cache, s.n_heads, s.scale, s.window, gate=gate, **self.mask)
+        attended = ctx.attend(q, k, v, cache, s.n_heads, s.scale, s.window, gate=None if s.gate_per_element else gate, **self.mask)
+        if s.gate_per_element:
+            kernels.sigmoid_gate(attended, gate)
         return linear(self.runtime, attended, self.out_w, self.out_b, residual=residual, out_dtype=residual.dtype,
                       out=residual)

@@ -1,12 +1,14 @@
 """Heads: from the residual stream to float32 logits at the wanted rows.
 
 'linear': the final norm on the wanted rows only, then logits = y . W^T (+ bias); W may be the embedding's
-table (damendaemon/gpt2.py:18,65-66: ``head is embed``, the norm after the last prompt row was picked).
+table (damendaemon/gpt2.py:18,65-66: ``head is embed``, the norm after the last prompt row was picked); with ``softcap`` c
+the logits become c * tanh(logits / c).
 """
 from __future__ import annotations
 
 import torch
 
+from .. import kernels
 from .interfaces import Head
 from .linear import linear
 from .registry import NORMS, lookup, register_head
@@ -32,4 +34,7 @@ class LinearHead(Head):
 
     def forward(self, x, ctx):
         y = self.norm.forward(x, row_index=ctx.want_rows)
-        return linear(self.runtime, y, self.weight, self.bias, out_dtype=torch.float32)
+        logits = linear(self.runtime, y, self.weight, self.bias, out_dtype=torch.float32)
+        if self.spec.softcap:
+            kernels.tanh_cap(logits, self.spec.softcap)
+        return logits

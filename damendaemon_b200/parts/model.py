@@ -4,7 +4,8 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from . import attention, block, delta_rule, embedding, feed_forward, head, latent_attention, norms, positions, retention  # noqa: F401  (register the built-in parts)
+from . import (attention, block, delta_rule, embedding, feed_forward, head, latent_attention, linear_recurrence, norms,  # noqa: F401
+               positions, retention, side_by_side, state_space)  # noqa: F401  (register the built-in parts)
 from .spec import TensorDecl
 from .registry import ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, lookup
 
@@ -22,6 +23,8 @@ def tensor_decls(spec):
     decls += lookup(HEADS, spec.head, "head").tensor_decls(spec.head)
     for stop, name in enumerate(spec.depth_mix or ()):
         decls.append(TensorDecl(name, (stop + 2,), "vector"))
+    if spec.pass_vectors is not None:
+        decls.append(TensorDecl(spec.pass_vectors[0], (spec.pass_vectors[1], spec.width), "vector"))
     unique = {}
     for d in decls:
         if d.name in unique and unique[d.name] != d:
@@ -32,7 +35,7 @@ def tensor_decls(spec):
 
 def cache_needs(spec):
     """One list of cache needs per stop of the run order: the mixer's (none for a stop that reads another's cache) and
-    the block arrangement's own (a state with a name)."""
+    the block arrangement's own (a state with a name); then, where the embedding has needs of its own, one more list with them."""
     needs = []
     for entry in spec.run_order:
         layer = spec.layers[entry.layer]
@@ -40,6 +43,10 @@ def cache_needs(spec):
         mine = [] if entry.cache_of is not None else list(lookup(MIXERS, mixer, "mixer").cache_needs(mixer))
         mine += getattr(lookup(ARRANGEMENTS, layer, "block arrangement"), "cache_needs", lambda _: [])(layer)
         needs.append(mine)
+    # one more site after the stops: the embedding's own per-request state, if it has any
+    own = list(getattr(lookup(EMBEDDINGS, spec.embedding, "embedding"), "cache_needs", lambda _: [])(spec.embedding))
+    if own:
+        needs.append(own)
     return needs
 
 
@@ -71,6 +78,16 @@ class DecoderModel:
             if len(spec.depth_mix) != len(spec.run_order):
                 raise ValueError(f"{len(spec.depth_mix)} depth weights for {len(spec.run_order)} stops of the run order")
             self.depth_mix = [weights[name] for name in spec.depth_mix]
+        self.pass_vectors = None
+        if spec.pass_vectors is not None:
+            self.pass_vectors = weights[spec.pass_vectors[0]]
+        for stop, entry in enumerate(spec.run_order):
+            if entry.add_vector is not None and (self.pass_vectors is None or not 0 <= entry.add_vector < self.pass_vectors.shape[0]):
+                raise ValueError(f"stop {stop} adds row {entry.add_vector} of a table the model does not have")
+        if spec.depth_mix is not None and any(e.add_embedding or e.add_vector is not None for e in spec.run_order):
+            raise ValueError("streams mixed over depth and stops that add to the stream do not go together")
+        self.keeps_embedding = any(e.add_embedding for e in spec.run_order)
+        self.embedding_has_state = bool(getattr(self.embedding, "cache_needs", lambda _: [])(spec.embedding))
         self.graph_safe = all(getattr(m, "graph_safe", False) for m in self.mixers) and \
             all(getattr(f, "graph_safe", False) for f in self.feed_forwards)
         # where the mixers like a prompt to be cut (a key block of a prompt attention kernel); 1: anywhere
@@ -79,13 +96,21 @@ class DecoderModel:
     def forward(self, ctx, caches):
         """Run the step's tokens; float32 logits [wanted rows, vocab] (or None if none are wanted).
 
-        caches: per stop of the run order, the LayerCache view its mixer reads (and writes, if it is its own).
+        caches: per stop of the run order, the LayerCache view its mixer reads (and writes, if it is its own); after
+        them the view of the embedding's own site.
         """
-        x = self.embedding.forward(ctx, self.position)
+        if self.embedding_has_state:
+            x = self.embedding.forward(ctx, self.position, caches[len(self.spec.run_order)])
+        else:
+            x = self.embedding.forward(ctx, self.position)
         if self.depth_mix is not None:
             x = self._forward_mixed_over_depth(x, ctx, caches)
         else:
+            first = x.clone() if self.keeps_embedding else None       # the blocks write the stream in place
             for stop, entry in enumerate(self.spec.run_order):
+                if entry.add_embedding or entry.add_vector is not None:
+                    kernels.add_rows(x, first if entry.add_embedding else None,
+                                     None if entry.add_vector is None else self.pass_vectors[entry.add_vector])
                 x = self.blocks[entry.layer].forward(x, ctx, caches[stop], self.position)
         if ctx.n_wanted == 0:
             return None

@@ -1,6 +1,7 @@
 """Norms. LayerNorm with weight and optional bias (damendaemon/starcoder.py:53-55); RMS norm,
 x / sqrt(mean(x^2) + eps) * (offset + weight), with the offset a parameter of the spec, and optionally in groups:
-the row in equal consecutive stretches, each divided by its own root mean square."""
+the row in equal consecutive stretches, each divided by its own root mean square; a norm without statistics,
+tanh(alpha x) * weight + bias with one learned number alpha."""
 from __future__ import annotations
 
 from .. import kernels
@@ -49,3 +50,23 @@ class RmsNorm(Norm):
         """The norm of every row blended with the norm of the token before it (kernels.rmsnorm_shift), one kernel."""
         return kernels.rmsnorm_shift(x, self.weight, self.spec.eps, self.runtime.dtype, shift, state, ctx.token_entry,
                                      ctx.entry_start, ctx.entry_slot, offset=self.spec.weight_offset, groups=self.spec.groups)
+
+
+@register_norm("tanh")
+class TanhNorm(Norm):
+    """tanh(alpha * x) * weight + bias: no mean, no variance, so a row needs no reduction."""
+
+    def __init__(self, spec, weights, runtime):
+        if not spec.bias or not spec.alpha:
+            raise ValueError("a tanh norm has a weight, a bias and the number alpha")
+        self.spec, self.runtime = spec, runtime
+        self.weight, self.bias = weights[spec.weight], weights[spec.bias]
+        self.alpha = weights[spec.alpha].reshape(1)
+
+    @staticmethod
+    def tensor_decls(spec):
+        return [TensorDecl(spec.weight, (spec.width,), "vector"), TensorDecl(spec.bias, (spec.width,), "vector"),
+                TensorDecl(spec.alpha, (), "vector")]
+
+    def forward(self, x, row_index=None, out_dtype=None):
+        return kernels.tanh_norm(x, self.alpha, self.weight, self.bias, out_dtype or self.runtime.dtype, row_index)

@@ -1,7 +1,7 @@
 """Position encodings. Learned absolute positions: a table added to the token embedding
 (damendaemon/gpt2.py:46); the add is fused into the embedding kernel. Rotary positions: queries and keys
 are rotated in place, pair by pair, by position x frequency, before they are cached and attended; the
-frequencies may be blended for a long context (``LongContextBlend``)."""
+frequencies may be blended for a long context (``LongContextBlend``) or stretched by wavelength (``WavelengthStretch``)."""
 from __future__ import annotations
 
 import math
@@ -11,7 +11,7 @@ import torch
 from .. import kernels
 from .interfaces import PositionEncoding
 from .registry import register_position
-from .spec import TensorDecl
+from .spec import TensorDecl, WavelengthStretch
 
 
 @register_position("learned")
@@ -35,7 +35,8 @@ class NoPositions(PositionEncoding):
 
 
 def rotary_frequencies(spec):
-    """(float64 frequencies [dims/2], factor on cosine and sine). Plain: f_i = base^(-2i/dims). Blended: see
+    """(float64 frequencies [dims/2], factor on cosine and sine). Plain: f_i = base^(-2i/dims). Stretched: see
+    ``WavelengthStretch``. Blended: see
     ``LongContextBlend``; the pair that turns t times over the original length is
     dims * ln(original / (2 pi t)) / (2 ln base)."""
     half = spec.dims // 2
@@ -43,6 +44,12 @@ def rotary_frequencies(spec):
     f = float(spec.base) ** (-2.0 * i / spec.dims)
     b = spec.blend
     if b is None:
+        return f, 1.0
+    if isinstance(b, WavelengthStretch):
+        length = 2 * math.pi / f
+        s = (b.original / length - b.low) / (b.high - b.low)
+        mixed = (1 - s) * f / b.factor + s * f
+        f = torch.where(length < b.original / b.high, f, torch.where(length > b.original / b.low, f / b.factor, mixed))
         return f, 1.0
     pair_of = lambda turns: spec.dims * math.log(b.original / (2 * math.pi * turns)) / (2 * math.log(spec.base))
     lo = max(math.floor(pair_of(b.fast)), 0)

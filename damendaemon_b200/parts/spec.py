@@ -36,7 +36,7 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str            # 'layernorm' | 'rmsnorm'
+    kind: str            # 'layernorm' | 'rmsnorm' | 'tanh' (tanh(alpha x) * weight + bias: no statistics, eps unused)
     width: int
     eps: float
     weight: str          # checkpoint names
@@ -44,6 +44,7 @@ class NormSpec:
     weight_offset: float = 0.0   # 'rmsnorm': the factor is weight_offset + weight (1 for a weight stored around zero)
     groups: int = 1              # 'rmsnorm': the row in this many equal consecutive stretches, each divided by its own
                                  # root mean square (the weight spans the whole row)
+    alpha: Optional[str] = None  # 'tanh': checkpoint name of the one number that multiplies x inside the tanh
 
 
 @dataclass(frozen=True)
@@ -67,13 +68,24 @@ class LongContextBlend:
 
 
 @dataclass(frozen=True)
+class WavelengthStretch:
+    """Rotary frequencies stretched for contexts beyond the one a model was trained at, by wavelength l = 2 pi / f: a pair
+    keeps f where l < original / high, gets f / factor where l > original / low, and between the two, with
+    s = (original / l - low) / (high - low), (1 - s) f / factor + s f. Cosine and sine are not scaled."""
+    factor: float
+    low: float
+    high: float
+    original: float
+
+
+@dataclass(frozen=True)
 class RotarySpec:
     kind: str            # 'rotary'
     head_dim: int
     dims: int            # the first `dims` dimensions of a head are rotated, the rest pass unchanged
     base: float
     interleaved: bool = True     # pairs are neighbours (2i, 2i+1); False: halves (i, i + dims/2)
-    blend: Optional[LongContextBlend] = None
+    blend: object = None         # None, a LongContextBlend or a WavelengthStretch
 
 
 @dataclass(frozen=True)
@@ -120,6 +132,16 @@ class AttentionSpec:
     # the softmax weights meet the values unrounded: a tensor-core kernel splits each into two bfloat16 terms instead of
     # rounding it to one (the float32 kernels do so anyway)
     exact_weights: bool = False
+    # the values are the keys as projected, before their norm and rotation: the mixer has no value projection (qkv_weight
+    # names the query and key projections only; value_dim must be head_dim)
+    values_are_keys: bool = False
+    # the norm of queries and of keys runs over the whole projection (all heads at once) instead of over every head;
+    # query_norm and key_norm then name weights [n_heads * head_dim] and [n_kv_heads * head_dim]
+    norm_whole_projection: bool = False
+    # the gate (gate_weight) has a row per element of the attended output, [n_heads * value_dim, width], instead of one per head
+    gate_per_element: bool = False
+    # one is added to the softmax's denominator (a sink whose score is 0 and that needs no tensor)
+    unit_sink: bool = False
 
 
 @dataclass(frozen=True)
@@ -202,6 +224,74 @@ class RetentionSpec:
     gate_weight: str
     out_weight: str
     rotary: object = None
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A state-space mixer with a scalar decay per head. W_in y = [z: inner | x: inner | B: groups * state | C: groups * state
+    | dt: n_heads] with inner = n_heads * value_dim; x, B and C together pass a short causal convolution per channel
+    (``conv_weight`` [channels, conv_taps], the last tap is the current token's, bias ``conv_bias``) and silu;
+    dt = softplus(dt + dt_bias). Per head h (group h // (n_heads / groups)), S [state, value_dim] float32 per request from
+    zero: S <- exp(-exp(A_log[h]) dt) S + dt B x^T, y = S^T C + D[h] x. y * silu(z) is divided, in ``norm_groups`` equal
+    stretches, by its root mean square (``norm_eps``), multiplied by ``out_norm`` [inner] and projected by W_out."""
+    kind: str            # 'state_space'
+    width: int
+    n_heads: int
+    value_dim: int
+    state: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    in_weight: str       # checkpoint names; matrices [out, in]
+    conv_weight: str
+    conv_bias: str
+    dt_bias: str
+    decay_log: str       # A_log [n_heads]
+    skip: str            # D [n_heads]
+    out_norm: str
+    out_weight: str
+
+
+@dataclass(frozen=True)
+class LinearRecurrenceSpec:
+    """A gated linear recurrence per channel. Two branches of ``inner`` channels: g = gelu_tanh(W_gate y + b) and
+    u = conv(W_in y + b), a short causal convolution per channel with a bias and no activation. The channels come in
+    ``blocks`` equal parts; in part p, r = sigmoid(Ra[p] u_p + ba[p]) and i = sigmoid(Ri[p] u_p + bi[p]);
+    a = exp(-gain * r * softplus(lam)); S <- a S + sqrt(1 - a^2) i u per channel, float32 per request from zero; the output
+    is W_out (S * g)."""
+    kind: str            # 'linear_recurrence'
+    width: int
+    inner: int
+    blocks: int
+    conv_taps: int
+    gain: float
+    gate_weight: str     # checkpoint names; matrices [out, in]
+    gate_bias: str
+    in_weight: str
+    in_bias: str
+    conv_weight: str
+    conv_bias: str
+    decay_gate: str      # Ra [blocks, part, part]
+    decay_gate_bias: str
+    input_gate: str      # Ri
+    input_gate_bias: str
+    decay_param: str     # lam [inner]
+    out_weight: str
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; the result is ``factor`` * (norm(left) * left_norm + norm(right) * right_norm),
+    each output divided by its root mean square over the model width (``norm_eps``) and multiplied by its weight [width]."""
+    kind: str            # 'side_by_side'
+    width: int
+    left: object         # mixer specs
+    right: object
+    left_norm: str       # checkpoint names
+    right_norm: str
+    norm_eps: float
+    factor: float = 0.5
 
 
 @dataclass(frozen=True)
@@ -309,6 +399,21 @@ class EmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class PairEmbeddingSpec:
+    """A row of the token table plus a row of a table of token pairs: row (previous id * mul_prev + id * mul_cur) mod buckets
+    of ``pair_table`` [buckets + 1, width]; a sequence's first token takes the last row. The id before a step's first token
+    is kept per request."""
+    kind: str            # 'tokens_pairs'
+    vocab_size: int
+    width: int
+    table: str           # checkpoint names
+    pair_table: str
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass(frozen=True)
 class HeadSpec:
     kind: str            # 'linear': final norm on the wanted rows, then logits = y . W^T (+ bias)
     vocab_size: int
@@ -317,6 +422,7 @@ class HeadSpec:
     weight: str          # checkpoint name of W [vocab, width]
     tied: bool = False   # W is the embedding's table (declared there, not again)
     bias: Optional[str] = None
+    softcap: Optional[float] = None   # c: logits become c * tanh(logits / c)
 
 
 @dataclass(frozen=True)
@@ -330,6 +436,10 @@ class RunEntry:
     """
     layer: int
     cache_of: Optional[int] = None
+    # before the stop runs (the start of a repeated pass over a run of layers): the embedding's output is added to the
+    # stream, and/or row ``add_vector`` of the model's ``pass_vectors`` table
+    add_embedding: bool = False
+    add_vector: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -347,6 +457,9 @@ class ModelSpec:
     # X_0 the embedding's output and X_(i+1) what stop i leaves, what stop i + 1 (and after the last stop the head)
     # reads is sum over j <= i + 1 of weights_i[j] * X_j
     depth_mix: Optional[Tuple[str, ...]] = None
+    # (checkpoint name, rows) of a float32 table [rows, width] whose rows stops of the run order add to the stream
+    # (RunEntry.add_vector)
+    pass_vectors: Optional[Tuple[str, int]] = None
     eos_token_ids: Tuple[int, ...] = ()
     ignored_tensors: Tuple[str, ...] = field(default_factory=tuple)   # regexes of tensors to drop
     tied_duplicates: Tuple[Tuple[str, str], ...] = field(default_factory=tuple)  # (name, must equal)

@@ -59,4 +59,4 @@ def load_config(model_dir):
 
 
 def _load_builtin():
-    from .architectures import bonatar, derusun, gpt2, zokanex  # noqa: F401  (register themselves on import)
+    from .architectures import bonatar, derusun, gpt2, tetitar, zokanex  # noqa: F401  (register themselves on import)
