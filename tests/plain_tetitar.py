@@ -28,6 +28,14 @@ _NP = {"F32": np.float32, "F64": np.float64, "F16": np.float16, "I32": np.int32,
 
 RECURRENCE_GAIN = 8.0         # the design fixes the factor in log a = -8 r softplus(lam)
 
+# None, or a dtype that stored activations are rounded to (what a 16-bit engine keeps between its kernels), so that a
+# test can measure how far such rounding alone moves the logits of a model
+ROUND = None
+
+
+def kept(x):
+    return x if ROUND is None else x.to(ROUND).to(x.dtype)
+
 
 def read_folder(folder, dtype=torch.float64):
     """(config dict, {name: tensor}); floating tensors as ``dtype``, integer tables as int64."""
@@ -59,7 +67,7 @@ def rms(x, eps):
 
 
 def tanh_norm(x, w, p):
-    return torch.tanh(w[p + ".alpha"] * x) * w[p] + w[p + ".b"]
+    return kept(torch.tanh(w[p + ".alpha"] * x) * w[p] + w[p + ".b"])
 
 
 def silu(x):
@@ -156,27 +164,27 @@ def full_attention(h, w, p, m, eps):
     T = h.shape[0]
     H, G, dk = m["heads"], m["kv_heads"], m["dim"]
     positions = torch.arange(T)
-    q, k = h @ w[p + "q"].T, h @ w[p + "k"].T
+    q, k = kept(h @ w[p + "q"].T), kept(h @ w[p + "k"].T)
     v = k.reshape(T, G, dk)
     q = (rms(q, eps) * w[p + "q.norm"]).reshape(T, H, dk)
     k = (rms(k, eps) * w[p + "k.norm"]).reshape(T, G, dk)
-    q, k = rotate_halves(q, positions, m["rot"]), rotate_halves(k, positions, m["rot"])
+    q, k = kept(rotate_halves(q, positions, m["rot"])), kept(rotate_halves(k, positions, m["rot"]))
     mask = m.get("mask")
     o = attend(q, k, v, m["scale"], visible(T, None if mask is None else mask["size"]), False)
-    return (o * torch.sigmoid(h @ w[p + "g"].T)) @ w[p + "o"].T
+    return kept(kept(o) * torch.sigmoid(kept(h @ w[p + "g"].T))) @ w[p + "o"].T
 
 
 def windowed_attention(h, w, p, m, eps):
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     positions = torch.arange(T)
-    q = (h @ w[p + "q"].T).reshape(T, H, dk)
-    k = (h @ w[p + "k"].T).reshape(T, G, dk)
-    v = (h @ w[p + "v"].T).reshape(T, G, dv)
+    q = kept(h @ w[p + "q"].T).reshape(T, H, dk)
+    k = kept(h @ w[p + "k"].T).reshape(T, G, dk)
+    v = kept(h @ w[p + "v"].T).reshape(T, G, dv)
     q, k = rms(q, eps) * w[p + "q.norm"], rms(k, eps) * w[p + "k.norm"]
-    q, k = rotate_halves(q, positions, m["rot"]), rotate_halves(k, positions, m["rot"])
+    q, k = kept(rotate_halves(q, positions, m["rot"])), kept(rotate_halves(k, positions, m["rot"]))
     mask = m.get("mask")
-    return attend(q, k, v, m["scale"], visible(T, None if mask is None else mask["size"]), True) @ w[p + "o"].T
+    return kept(attend(q, k, v, m["scale"], visible(T, None if mask is None else mask["size"]), True)) @ w[p + "o"].T
 
 
 def state_space(h, w, p, m, eps):
@@ -184,7 +192,7 @@ def state_space(h, w, p, m, eps):
     T = h.shape[0]
     H, dv, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner = H * dv
-    proj = h @ w[p + "in"].T
+    proj = kept(h @ w[p + "in"].T)
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
     xbc = silu(causal_convolution(xbc, w[p + "conv"], w[p + "conv.b"]))
     x = xbc[:, :inner].reshape(T, H, dv)
@@ -201,7 +209,7 @@ def state_space(h, w, p, m, eps):
     y = y.reshape(T, inner) * silu(z)
     parts = m["norm_groups"]
     y = rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * w[p + "norm"]
-    return y @ w[p + "o"].T
+    return kept(y) @ w[p + "o"].T
 
 
 def side_by_side(h, w, p, m, eps):
@@ -215,8 +223,8 @@ def gated_recurrence(h, w, p, m, eps):
     a = exp(-8 r softplus(lam)); S <- a S + sqrt(1 - a^2) i u from zero; out = W_o (S y)."""
     T = h.shape[0]
     width, blocks = m["width"], m["blocks"]
-    y = gelu_tanh(h @ w[p + "y"].T + w[p + "y.b"])
-    u = causal_convolution(h @ w[p + "x"].T + w[p + "x.b"], w[p + "conv"], w[p + "conv.b"])
+    y = gelu_tanh(kept(h @ w[p + "y"].T + w[p + "y.b"]))
+    u = causal_convolution(kept(h @ w[p + "x"].T + w[p + "x.b"]), w[p + "conv"], w[p + "conv.b"])
     ub = u.reshape(T, blocks, width // blocks)
     r = torch.sigmoid(torch.einsum("boi,tbi->tbo", w[p + "ra"], ub) + w[p + "ra.b"]).reshape(T, width)
     i = torch.sigmoid(torch.einsum("boi,tbi->tbo", w[p + "ri"], ub) + w[p + "ri.b"]).reshape(T, width)
@@ -227,11 +235,11 @@ def gated_recurrence(h, w, p, m, eps):
     for t in range(T):
         S = a[t] * S + drive[t]
         out[t] = S
-    return (out * y) @ w[p + "o"].T
+    return kept(out * y) @ w[p + "o"].T
 
 
 def silu_unit(h, w, p):
-    return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
+    return kept(silu(kept(h @ w[p + "gate"].T)) * kept(h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 MIXERS = {"attention": full_attention, "parallel": side_by_side, "rglru": gated_recurrence}
