@@ -363,6 +363,17 @@ DERUSUN_KERNEL_PAIRS = [     # (a kernel of Derusun, the like kernel of the clos
     ("sinks_decode_b64_c768", "attn_decode_b64_masked"),
     ("sinks_prefillrows_p2_t1024", "attn_prefill_p2_t1024_masked"), ("sinks_decoderows_b8_c768", "attn_decode_rows_b8_masked"),
 ]
+TETITAR_KERNEL_PAIRS = [     # (a kernel of Tetitar, the like kernel of the closest model, Zokanex) at width 1600, 25 heads of 64
+    ("tanhnorm_m2048", "rmsnorm_m2048"), ("tanhnorm_m8", "rmsnorm_m8"), ("widenorm_m2048", "headnorm_m2048"), ("widenorm_m8", "headnorm_m8"),
+    ("ssmscan_p2_t1024", "retention_p2_t1024"), ("ssmscan_p8_t1", "retention_p8_t1"), ("ssmscan_p64_t1", "retention_p64_t1"),
+    ("ssmconv_p2_t1024", None), ("ssmconv_p8_t1", None), ("ssmfinish_p2_t1024", "retfinish_p2_t1024"), ("ssmfinish_p8_t1", "retfinish_p8_t1"),
+    ("rglrugates_p2_t1024", "gemm32_proj_m2048"), ("rglrugates_p8_t1", "gemm32_proj_m8"),
+    ("rglruscan_p2_t1024", "retention_p2_t1024"), ("rglruscan_p8_t1", "retention_p8_t1"), ("rglruscan_p64_t1", "retention_p64_t1"),
+    ("unitsink_prefill_p2_t1024", "attn_prefill_p2_t1024_masked"), ("unitsink_decode_b8_c768", "attn_decode_rows_b8_masked"),
+    ("unitsink_decode_b64_c768", "attn_decode_b64_masked"),
+    ("sigmoidgate_m2048", "gatedact_m2048"), ("sigmoidgate_m8", "gatedact_m8"), ("pairnorm_m2048", "rmsnorm_m2048"), ("pairnorm_m8", "rmsnorm_m8"),
+    ("embedpairs_m2048", None), ("embedpairs_m8", None),
+]
 CUDA_CORE_FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12      # nominal: 148 SMs x 128 lanes x one fused multiply-add a cycle at 1,965 MHz
 
 
@@ -417,6 +428,38 @@ def derusun_configs(size, layers, vocab=50257):
     return out
 
 
+def tetitar_configs(size, layers, vocab=50257):
+    """Zokanex (attention layers; retention layers) and Tetitar models whose layers have one size, each with the silu gated
+    unit: layers of attention whose values are its keys (norm over the whole projection, stretched rotation, a gate per
+    element); parallel layers (windowed attention with a unit term beside a state-space mixer of 25 heads of 64 by 64); layers
+    of the gated linear recurrence (ten parts); and a recurrence layer, then an attention and a parallel layer that run twice,
+    then an attention layer (four layers, six runs)."""
+    z = DESIGN_SIZES[size]
+    out = {k: v for k, v in zokanex_configs(size, layers, vocab).items() if k in ("zokanex_attention_dense", "zokanex_retention_dense")}
+    heads, width = z["heads"], z["width"]
+    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}
+    attention = {"heads": heads, "kv_heads": heads, "dim": 64, "vdim": 64, "scale": 0.125, "rot": rot}
+    left = {"heads": heads, "kv_heads": heads, "dim": 64, "vdim": 64, "scale": 0.125, "rot": {"dims": 64, "base": 10000.0}, "mask": {"size": 1024}}
+    right = {"heads": heads, "vdim": 64, "state": 64, "groups": 1, "conv": 4, "norm_groups": 1}
+    recurrence = {"width": width, "blocks": heads if width % 10 else 10, "conv": 4}
+    dense = {"kind": "dense", "ff": z["ff"]}
+
+    def model(entries, loop=None):
+        config = {"architecture": "Tetitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+                  "embedding": {"bigram": {"buckets": 99991, "mul_prev": 31, "mul_cur": 17}},
+                  "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in entries]}
+        if loop:
+            config["loop"] = dict(zip(("start", "stop", "times"), loop))
+        return config
+    parallel = {"left": left, "right": right}
+    out["tetitar_attention_dense"] = model([("attention", attention, dense)] * layers)
+    out["tetitar_parallel_dense"] = model([("parallel", parallel, dense)] * layers)
+    out["tetitar_recurrence_dense"] = model([("rglru", recurrence, dense)] * layers)
+    out["tetitar_looped_mix"] = model([("rglru", recurrence, dense), ("attention", attention, dense), ("parallel", parallel, dense),
+                                       ("attention", attention, dense)], loop=(1, 3, 2))
+    return out
+
+
 def design_configs(size, layers, vocab=50257):
     """GPT-2 and two Bonatar models (dense layers only; expert layers only) whose layers have one size."""
     z = DESIGN_SIZES[size]
@@ -433,8 +476,8 @@ def design_configs(size, layers, vocab=50257):
 
 
 def design_bench(args):
-    """``--design bonatar`` (beside GPT-2), ``--design zokanex`` (beside Bonatar, the closest model) or ``--design derusun``
-    (beside Zokanex, the closest model): prefill and decode
+    """``--design bonatar`` (beside GPT-2), ``--design zokanex`` (beside Bonatar, the closest model), ``--design derusun`` or
+    ``--design tetitar`` (each beside Zokanex, the closest model): prefill and decode
     throughput at equal layer sizes (random
     bfloat16 weights, a few layers), and each kernel of the new design beside the like kernel of the other, timed in a
     chain replayed from a CUDA graph over inputs that rotate through more memory than L2 holds."""
@@ -444,6 +487,7 @@ def design_bench(args):
     hbm, tflops = measured_peaks["hbm_gbs"], measured_peaks["bf16_tflops"]
     layers = args.layers or 6
     configs_of, pairs = {"zokanex": (zokanex_configs, ZOKANEX_KERNEL_PAIRS), "derusun": (derusun_configs, DERUSUN_KERNEL_PAIRS),
+                         "tetitar": (tetitar_configs, TETITAR_KERNEL_PAIRS),
                          "bonatar": (design_configs, DESIGN_KERNEL_PAIRS)}[args.design]
     out = {"design": args.design, "layers": layers, "dtype": "bf16", "data": "synthetic", "peaks": dict(measured_peaks, source=peaks_from),
            "sizes": {}, "kernels": [],
@@ -527,7 +571,7 @@ def main():
     parser.add_argument("--case-iters", type=int, default=50)
     parser.add_argument("--case-graph", action="store_true", help="time the kernel case as launches replayed from one CUDA graph")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
-    parser.add_argument("--design", choices=("bonatar", "zokanex", "derusun"), help="another design beside GPT-2 (zokanex: beside Bonatar; derusun: beside Zokanex) at equal layer sizes (prefill, decode, "
+    parser.add_argument("--design", choices=("bonatar", "zokanex", "derusun", "tetitar"), help="another design beside GPT-2 (zokanex: beside Bonatar; derusun and tetitar: beside Zokanex) at equal layer sizes (prefill, decode, "
                         "kernel by kernel) instead of the headline bench")
     parser.add_argument("--parity", action="store_true", help="the float32 engine beside the bfloat16 one: on the benchmark's model "
                         "(logit differences, greedy agreement), or with --workload on that workload (the same requests in both)")

@@ -278,7 +278,7 @@ def _per_head_case(rows, dev, up, kernel=None):
     return run, {"bytes": rows * H * (D + ROT + RANK + ROT) * 2 + w.numel() * 2, "flops": 2 * rows * H * D * RANK}
 
 
-def _sinks_case(batch, length, dev, decode, kernel):
+def _sinks_case(batch, length, dev, decode, kernel, unit_only=False):
     """Attention with a window that keeps the first keys, capped scores and a sink (25 heads of 64): prompts through the
     mma.sync kernel or single tokens through the row decode kernel ('tensor'), or either through the general kernel
     ('rows'). The window holds the whole context, so the same keys are read as in the plain cases."""
@@ -288,13 +288,16 @@ def _sinks_case(batch, length, dev, decode, kernel):
     caches, table = _cache_case(batch, context, dev, copies)
     q = torch.randn(tokens, H * D, device=dev).to(torch.bfloat16)
     kw = dict(window=1024 * ((context + 1023) // 1024), keep_first=4, softcap=30.0, sink=torch.zeros(H, device=dev))
+    exact = True
+    if unit_only:        # a window and one added to the softmax's denominator, nothing else
+        kw, exact = dict(window=kw["window"], sink=kw["sink"]), False
     if decode:
         ent = torch.arange(batch, dtype=torch.int32, device=dev)
         pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
         splits = max(1, min(-(-(K.sm_count(dev) * 2) // (batch * H)), (context + 127) // 128, 32))
         work = {"bytes": batch * context * H * D * 4, "flops": 4 * batch * context * H * D}
         if kernel == "tensor":
-            run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, n_splits=splits, exact_weights=True, **kw)
+            run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, n_splits=splits, exact_weights=exact, **kw)
         else:
             run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, D ** -0.5, n_splits=splits, **kw)
         return run, work
@@ -302,12 +305,123 @@ def _sinks_case(batch, length, dev, decode, kernel):
     pos0 = torch.zeros(batch, dtype=torch.int32, device=dev)
     work = {"bytes": batch * length * H * D * 6, "flops": batch * 4 * (length * (length + 1) // 2) * H * D}
     if kernel == "tensor":
-        run = lambda i: K.attention_prefill(q, caches[i % copies], start, pos0, table, H, D ** -0.5, exact_weights=True, **kw)
+        run = lambda i: K.attention_prefill(q, caches[i % copies], start, pos0, table, H, D ** -0.5, exact_weights=exact, **kw)
     else:
         ent = torch.arange(tokens, dtype=torch.int32, device=dev) // length
         pos = torch.arange(tokens, dtype=torch.int32, device=dev) % length
         run = lambda i: K.attention_rows(q, caches[i % copies], ent, pos, table, H, D ** -0.5, **kw)
     return run, work
+
+
+def _entries(entries, length, dev):
+    tokens = entries * length
+    ent = torch.arange(tokens, dtype=torch.int32, device=dev) // length
+    start = torch.arange(entries + 1, dtype=torch.int32, device=dev) * length
+    return tokens, ent, start, torch.arange(entries, dtype=torch.int32, device=dev)
+
+
+def _tanh_norm_case(rows, dev):
+    """The norm without statistics, tanh(alpha x) w + b, of `rows` rows of the float32 stream (width 1600) into bfloat16."""
+    width = 1600
+    copies = max(2, min(24, (300 << 20) // (rows * width * 4)))
+    xs = [torch.randn(rows, width, device=dev) for _ in range(copies)]
+    alpha, w, b = torch.full((1,), 0.5, device=dev), torch.ones(width, device=dev), torch.zeros(width, device=dev)
+    out = torch.empty(rows, width, device=dev, dtype=torch.bfloat16)
+    run = lambda i: K.tanh_norm(xs[i % copies], alpha, w, b, torch.bfloat16, out=out)
+    return run, {"bytes": rows * width * 6, "flops": 10 * rows * width}
+
+
+def _wide_norm_case(rows, dev):
+    """Queries and keys of `rows` tokens (25 + 25 heads of 64) normed over the whole projection and rotated in halves."""
+    copies = max(2, min(24, (300 << 20) // (rows * 3 * H * D * 2)))
+    bufs = [torch.randn(rows, 3 * H * D + 32, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    pos = torch.arange(rows, dtype=torch.int32, device=dev) % 1024
+    freqs = (10000.0 ** (-torch.arange(D // 2, dtype=torch.float64) * 2 / D)).float().to(dev)
+    wq, wk = torch.ones(H * D, device=dev), torch.ones(H * D, device=dev)
+    run = lambda i: K.wide_norm_rotary(bufs[i % copies][:, :H * D], bufs[i % copies][:, H * D:2 * H * D], pos, wq, wk, 1e-6, H, H, D,
+                                       freqs=freqs, interleaved=False)
+    return run, {"bytes": rows * 2 * H * D * 4, "flops": 10 * rows * H * D}
+
+
+STATE = 64          # rows of the state-space mixer's state: 25 heads of 64 by 64, the size of a retention head
+
+
+def _state_space_case(entries, length, dev, which):
+    """The state-space mixer of `entries` requests of `length` tokens each in one step (25 heads with values of 64 and a
+    state of 64 rows, one group, four taps): 'conv' the convolution with silu over [x | B | C], 'scan' the recurrence over
+    the float32 state, 'finish' the gate, the norm and the weight of the read-out."""
+    tokens, ent, start, slot = _entries(entries, length, dev)
+    inner, channels = H * D, H * D + 2 * STATE
+    copies = max(2, min(24, (300 << 20) // max(1, tokens * (2 * inner + channels) * 2 + entries * H * D * STATE * 4)))
+    bufs = [torch.randn(tokens, inner + channels + H + 7, device=dev).mul_(0.5).to(torch.bfloat16) for _ in range(copies)]
+    if which == "conv":
+        taps, bias = torch.randn(channels, 4, device=dev) * 0.5, torch.zeros(channels, device=dev)
+        state = torch.zeros(entries, 3, channels, device=dev)
+        out = torch.empty(tokens, channels, device=dev)
+        run = lambda i: K.conv_channels(bufs[i % copies][:, inner:inner + channels], taps, bias, state, ent, start, slot, activation="silu", out=out)
+        return run, {"bytes": tokens * channels * 6, "flops": 12 * tokens * channels}
+    if which == "finish":
+        y, w = torch.randn(tokens, inner, device=dev), torch.ones(inner, device=dev)
+        out = torch.empty(tokens, inner, device=dev, dtype=torch.bfloat16)
+        run = lambda i: K.gated_group_norm(y, bufs[i % copies][:, :inner], w, 1, 1e-6, torch.bfloat16, out=out)
+        return run, {"bytes": tokens * inner * 8, "flops": 8 * tokens * inner}
+    xbc = [torch.randn(tokens, channels, device=dev).mul_(0.5) for _ in range(min(copies, 6))]
+    states = [torch.zeros(entries, *K.state_space_state_shape(H, STATE, D), device=dev) for _ in range(copies)]
+    dt_bias, a_log, skip = torch.zeros(H, device=dev), torch.full((H,), -3.0, device=dev), torch.ones(H, device=dev)
+    out = torch.empty(tokens, inner, device=dev)
+
+    def run(i):
+        K.state_space_scan(xbc[i % len(xbc)], bufs[i % copies][:, inner + channels:inner + channels + H], dt_bias, a_log, skip, start, slot,
+                           states[i % copies], H, 1, STATE, D, out=out)
+    return run, {"bytes": entries * H * D * STATE * 8 + tokens * (channels * 4 + inner * 4), "flops": 4 * tokens * H * D * STATE, "fp32": True}
+
+
+def _recurrence_case(entries, length, dev, which):
+    """The gated linear recurrence of `entries` requests of `length` tokens (1,600 channels in ten parts of 160): 'gates' the
+    two float32 products of every part with their sigmoids, the decay and the drive; 'scan' the walk over the tokens with the
+    tanh-gelu branch multiplied in."""
+    tokens, ent, start, slot = _entries(entries, length, dev)
+    width, blocks = 1600, 10
+    part = width // blocks
+    copies = max(2, min(24, (300 << 20) // (tokens * width * 8)))
+    us = [torch.randn(tokens, width, device=dev) for _ in range(copies)]
+    if which == "gates":
+        wa, wi = (torch.randn(blocks, part, part, device=dev) / part ** 0.5 for _ in range(2))
+        ba, bi, lam = torch.zeros(width, device=dev), torch.zeros(width, device=dev), torch.full((width,), -2.0, device=dev)
+        run = lambda i: K.recurrence_gates(us[i % copies], wa, ba, wi, bi, lam, 8.0)
+        return run, {"bytes": tokens * width * 12 + 2 * width * part * 4, "flops": 4 * tokens * width * part, "fp32": True}
+    fade, y = torch.rand(tokens, width, device=dev) * 0.1, torch.randn(tokens, width + 8, device=dev).to(torch.bfloat16)
+    state = torch.zeros(entries, width, device=dev)
+    out = torch.empty(tokens, width, device=dev, dtype=torch.bfloat16)
+    run = lambda i: K.linear_scan(fade, us[i % copies], y[:, :width], start, slot, state, activation="gelu_tanh", out=out)
+    return run, {"bytes": tokens * width * 12 + entries * width * 8, "flops": 12 * tokens * width, "fp32": True}
+
+
+def _row_ops_case(which, rows, dev):
+    """'gate': the attended rows (25 heads of 64) times the sigmoid of a gate per element; 'pairnorm': two float32 results of
+    width 1600, each RMS-normed and weighted, averaged into the stream; 'embedpairs': the token's row plus the row of its
+    pair with the token before, into the float32 stream."""
+    width = 1600
+    copies = max(2, min(24, (300 << 20) // (rows * width * 8)))
+    if which == "gate":
+        bufs = [torch.randn(rows, 2 * H * D, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        run = lambda i: K.sigmoid_gate(bufs[i % copies][:, :H * D], bufs[i % copies][:, H * D:])
+        return run, {"bytes": rows * H * D * 6, "flops": 6 * rows * H * D}
+    if which == "pairnorm":
+        both = [torch.randn(2, rows, width, device=dev) for _ in range(copies)]
+        x, wl, wr = torch.zeros(rows, width, device=dev), torch.ones(width, device=dev), torch.ones(width, device=dev)
+        run = lambda i: K.norm_pair_add(x, both[i % copies][0], both[i % copies][1], wl, wr, 1e-6, 0.5)
+        return run, {"bytes": rows * width * 16, "flops": 10 * rows * width}
+    vocab, buckets = 50257, 99991
+    table, pairs = torch.randn(vocab, width, device=dev).to(torch.bfloat16), torch.randn(buckets + 1, width, device=dev).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (rows,), dtype=torch.int32, device=dev)
+    n = max(1, rows // 1024) if rows >= 1024 else rows
+    tokens, ent, start, slot = _entries(n, rows // n, dev)
+    pos = torch.arange(rows, dtype=torch.int32, device=dev) % (rows // n) + 1
+    last = torch.zeros(n, dtype=torch.int32, device=dev)
+    out = torch.empty(rows, width, device=dev)
+    run = lambda i: K.embed_pairs(ids, pos, ent, start, slot, table, pairs, last, 31, 17, out=out)
+    return run, {"bytes": rows * width * 8, "flops": 2 * rows * width}
 
 
 def _gated_act_case(rows, dev):
@@ -414,13 +528,32 @@ def build(name, device="cuda:0"):
     retfinish_p<requests>_t<tokens> | groupnorm_m<rows> | depthmix_m<rows> | delta_p<requests>_t<tokens> | deltaprep_p.._t.. |
     deltafinish_p.._t.. | latent_prefill_p<prompts>_t<tokens> | latent_decode_b<batch>_c<context> | latentprep_m<rows> |
     perhead_m<rows> | perheadup_m<rows> | sinks_prefill_p<prompts>_t<tokens> | sinks_decode_b<batch>_c<context> (and
-    sinks_prefillrows_.., sinks_decoderows_..: through the general kernel); attention cases take the suffix _masked (a chunked mask and a gate on every head's
+    sinks_prefillrows_.., sinks_decoderows_..: through the general kernel) | tanhnorm_m<rows> | widenorm_m<rows> |
+    ssmconv_p<requests>_t<tokens> | ssmscan_p.._t.. | ssmfinish_p.._t.. | rglrugates_p.._t.. | rglruscan_p.._t.. |
+    sigmoidgate_m<rows> | pairnorm_m<rows> | embedpairs_m<rows> | unitsink_prefill_p<prompts>_t<tokens> |
+    unitsink_decode_b<batch>_c<context>; attention cases take the suffix _masked (a chunked mask and a gate on every head's
     output)"""
     K.library("core"), K.library("tensor")
     masked = name.endswith("_masked")          # attention cases: with a chunked mask and an output gate
     if masked:
         name = name[:-len("_masked")]
     parts = name.split("_")
+    if name.startswith("tanhnorm_m"):
+        return _tanh_norm_case(int(name[len("tanhnorm_m"):]), device)
+    if name.startswith("widenorm_m"):
+        return _wide_norm_case(int(name[len("widenorm_m"):]), device)
+    if parts[0] in ("ssmconv", "ssmscan", "ssmfinish", "rglrugates", "rglruscan") and "_p" in name:
+        # ssmconv_p<requests>_t<tokens of each> | ssmscan_.. | ssmfinish_.. | rglrugates_.. | rglruscan_..
+        entries, tokens = name.split("_p")[1].split("_t")
+        if parts[0].startswith("ssm"):
+            return _state_space_case(int(entries), int(tokens), device, parts[0][3:])
+        return _recurrence_case(int(entries), int(tokens), device, parts[0][5:])
+    if parts[0] in ("sigmoidgate", "pairnorm", "embedpairs") and len(parts) == 2 and parts[1][0] == "m":
+        return _row_ops_case({"sigmoidgate": "gate"}.get(parts[0], parts[0]), int(parts[1][1:]), device)
+    if parts[0] == "unitsink" and parts[1] in ("prefill", "decode"):
+        # unitsink_prefill_p<prompts>_t<tokens> | unitsink_decode_b<batch>_c<context>: a window and a unit term in the softmax
+        a, b = name.split("_", 2)[2][1:].replace("_t", " ").replace("_c", " ").split()
+        return _sinks_case(int(a), int(b), device, parts[1] == "decode", "tensor", unit_only=True)
     if name.startswith("groupnorm_m"):
         return _group_norm_shift_case(int(name[len("groupnorm_m"):]), device)
     if name.startswith("depthmix_m"):
