@@ -304,7 +304,12 @@ def _sinks_case(batch, length, dev, decode, kernel, unit_only=False):
     start = torch.arange(batch + 1, dtype=torch.int32, device=dev) * length
     pos0 = torch.zeros(batch, dtype=torch.int32, device=dev)
     work = {"bytes": batch * length * H * D * 6, "flops": batch * 4 * (length * (length + 1) // 2) * H * D}
-    if kernel == "tensor":
+    if kernel == "tensor" and unit_only:
+        # the tcgen05 prompt kernel takes a sink alone; keys and values of the step as the fused projection leaves them
+        qkv = torch.randn(tokens, 3 * H * D, device=dev).to(torch.bfloat16)
+        run = lambda i: K.attention_prefill(qkv[:, :H * D], caches[i % copies], start, pos0, table, H, D ** -0.5, kernel="tcgen05",
+                                            k_new=qkv[:, H * D:2 * H * D], v_new=qkv[:, 2 * H * D:], **kw)
+    elif kernel == "tensor":
         run = lambda i: K.attention_prefill(q, caches[i % copies], start, pos0, table, H, D ** -0.5, exact_weights=exact, **kw)
     else:
         ent = torch.arange(tokens, dtype=torch.int32, device=dev) // length

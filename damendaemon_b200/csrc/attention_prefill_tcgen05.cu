@@ -52,6 +52,7 @@ struct AttnParams {
     int chunk;                   // > 0: a query sees only the keys of its own chunk of this many positions (from position 0)
     const __nv_bfloat16* gate;   // null, or rows of gate_stride elements, one per head: sigmoid(gate) multiplies the head's output
     int gate_stride;
+    const float* sink;           // null, or one float32 per head: exp(sink) joins the softmax's denominator (a key without a value)
     float scale_log2e;
     int new_rows;                   // 1: this step's keys and values are also at hand as rows beside the queries
     int store_new;                  // 1: the kernel itself puts those rows into the cache (every entry starts on a key-block boundary)
@@ -460,6 +461,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (j_last - j_first) & 1, abort_flag));
         if (alive) {
             tc::fence_after_sync();
+            // (the running maximum m is in units of log2; a query always sees its own key, so m is finite here)
+            if (p.sink) l += exp2f(p.sink[h] * 1.4426950408889634f - m);
             float inv = l > 0.f ? 1.f / l : 0.f;
             if (p.gate && r < rows)
                 inv *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t)(row0 + t * BQ + r) * p.gate_stride + h])));
@@ -543,11 +546,12 @@ DD_API int dd_attention_prefill_tcgen05_supported(int n_heads, int n_kv_heads, i
 // that breaks it sets error bit 2 and writes nothing).
 // chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0). gate: null,
 // or rows of gate_stride bf16 with one element per head, whose logistic function multiplies the head's output.
-DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* k_new, const void* v_new, int store_new, void* cache, const int* entry_start,
-                                        const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
-                                        int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads,
-                                        int head_dim, int page_size, int n_pages, int window, float scale,
-                                        int* error_flag, void* stream, int chunk, const void* gate, int gate_stride) {
+// sink: null, or float32 [n_heads]: exp(sink) joins every row's denominator.
+DD_API int dd_attention_prefill_tcgen05_sink(const void* q, int q_stride, const void* k_new, const void* v_new, int store_new, void* cache, const int* entry_start,
+                                             const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
+                                             int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads,
+                                             int head_dim, int page_size, int n_pages, int window, float scale,
+                                             int* error_flag, void* stream, int chunk, const void* gate, int gate_stride, const float* sink) {
     if (n_tokens <= 0 || n_entries <= 0) return 0;
     if (!dd_attention_prefill_tcgen05_supported(n_heads, n_kv_heads, head_dim, page_size, DD_BF16))
         return dd_fail("dd_attention_prefill_tcgen05: needs head size 64, pages of 8 to 128 tokens (a power of two) and heads a "
@@ -579,11 +583,21 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     p.out = (__nv_bfloat16*)out; p.error_flag = error_flag;
     p.n_entries = n_entries; p.max_blocks = max_blocks; p.out_stride = out_stride; p.H = n_heads; p.KH = n_kv_heads;
     p.P = page_size; p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
-    p.chunk = chunk; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
+    p.chunk = chunk; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride; p.sink = sink;
     p.new_rows = k_new != nullptr;
     p.store_new = store_new != 0;
     // an upper bound of the number of pairs of 128-row tiles; blocks beyond the real count return at once
     dim3 grid(n_heads, dd_ceil_div(n_tokens, TILES * BQ) + n_entries);
     dd_launch(attention_prefill_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv, map_k_new, map_v_new, p);
     return dd_check_launch("dd_attention_prefill_tcgen05");
+}
+
+DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* k_new, const void* v_new, int store_new, void* cache, const int* entry_start,
+                                        const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
+                                        int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads,
+                                        int head_dim, int page_size, int n_pages, int window, float scale,
+                                        int* error_flag, void* stream, int chunk, const void* gate, int gate_stride) {
+    return dd_attention_prefill_tcgen05_sink(q, q_stride, k_new, v_new, store_new, cache, entry_start, entry_pos0, n_entries, n_tokens,
+                                             block_table, max_blocks, out, out_stride, n_heads, n_kv_heads, head_dim, page_size, n_pages,
+                                             window, scale, error_flag, stream, chunk, gate, gate_stride, nullptr);
 }

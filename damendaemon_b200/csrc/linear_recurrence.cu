@@ -73,6 +73,8 @@ recurrence_gates_kernel(const float* __restrict__ u, const float* __restrict__ w
     }
 }
 
+constexpr int LS_TOKENS = 16;     // tokens whose operands a thread of the scan requests together
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ a, const float* __restrict__ drive, const T* __restrict__ y, int y_stride,
@@ -85,15 +87,83 @@ linear_scan_kernel(const float* __restrict__ a, const float* __restrict__ drive,
     float* sp = state + (size_t)entry_slot[e] * width + c;
     dd_grid_wait();
     float s = *sp;
-#pragma unroll 4
-    for (int t = start; t < end; ++t) {
-        const size_t at = (size_t)t * width + c;
-        s = fmaf(-a[at], s, s) + drive[at];              // a holds 1 - decay
-        float g = dd_to_f32(y[(size_t)t * y_stride + c]);
-        if (act == 1) g = dd_activation(g, DD_ACT_GELU_NEW);
-        out[(size_t)t * out_stride + c] = dd_from_f32<T>(s * g);
+    // the operands of the next LS_TOKENS tokens are requested before this chunk's chain of multiply-adds runs: the walk
+    // is bound by the loads' latency, not by arithmetic
+    float fa[LS_TOKENS], fd[LS_TOKENS], fy[LS_TOKENS];
+    auto fetch = [&](int t0) {
+#pragma unroll
+        for (int k = 0; k < LS_TOKENS; ++k) {
+            const int t = min(t0 + k, end - 1);
+            fa[k] = a[(size_t)t * width + c];
+            fd[k] = drive[(size_t)t * width + c];
+            fy[k] = dd_to_f32(y[(size_t)t * y_stride + c]);
+        }
+    };
+    if (start < end) fetch(start);
+    for (int t0 = start; t0 < end; t0 += LS_TOKENS) {
+        float ca[LS_TOKENS], cd[LS_TOKENS], cy[LS_TOKENS];
+#pragma unroll
+        for (int k = 0; k < LS_TOKENS; ++k) { ca[k] = fa[k]; cd[k] = fd[k]; cy[k] = fy[k]; }
+        if (t0 + LS_TOKENS < end) fetch(t0 + LS_TOKENS);
+#pragma unroll
+        for (int k = 0; k < LS_TOKENS; ++k) {
+            if (t0 + k < end) {
+                s = fmaf(-ca[k], s, s) + cd[k];              // a holds 1 - decay
+                const float g = act == 1 ? dd_activation(cy[k], DD_ACT_GELU_NEW) : cy[k];
+                out[(size_t)(t0 + k) * out_stride + c] = dd_from_f32<T>(s * g);
+            }
+        }
     }
     *sp = s;
+}
+
+// A step of few tokens: a warp owns one token and 32 output channels of one part, a lane one channel, whose two weight rows it
+// streams in 16-byte pieces (the warps of a block read the same rows, from L1 after the first); the part's inputs of all the
+// step's tokens lie in shared memory. The sums run over the input channels in ascending order, the same multiply-adds in the
+// same order as in the tiled kernel, so a token's gates do not depend on which kernel computed them.
+constexpr int RG_FEW = 16, RG_FEW_OUTS = 32;
+
+__global__ void __launch_bounds__(RG_FEW * RG_FEW_OUTS)
+recurrence_gates_few_kernel(const float* __restrict__ u, const float* __restrict__ wa, const float* __restrict__ ba,
+                            const float* __restrict__ wi, const float* __restrict__ bi, const float* __restrict__ lam, float gain,
+                            float* __restrict__ a_out, float* __restrict__ drive_out, int n_tokens, int width, int bw) {
+    extern __shared__ float us[];                   // [n_tokens][bw]
+    dd_launch_dependents();
+    const int b = blockIdx.y, j = threadIdx.x >> 5, o = blockIdx.x * RG_FEW_OUTS + (threadIdx.x & 31);
+    const bool live = o < bw;
+    const float* ra_row = wa + ((size_t)b * bw + (live ? o : 0)) * bw;
+    const float* ri_row = wi + ((size_t)b * bw + (live ? o : 0)) * bw;
+    const float bias_a = live ? ba[b * bw + o] : 0.f, bias_i = live ? bi[b * bw + o] : 0.f;
+    const float sp = live ? rg_softplus(lam[b * bw + o]) : 0.f;
+    dd_grid_wait();
+    for (int i = threadIdx.x; i < n_tokens * bw; i += blockDim.x) us[i] = u[(size_t)(i / bw) * width + b * bw + i % bw];
+    __syncthreads();
+    if (!live) return;
+    const float* mine = us + j * bw;
+    float ra = 0.f, ri = 0.f;
+    const bool wide = (bw & 3) == 0;
+    for (int k = 0; k < bw; k += 4) {
+        float a4[4], i4[4];
+        if (wide) {
+            const float4 x = *reinterpret_cast<const float4*>(ra_row + k), z = *reinterpret_cast<const float4*>(ri_row + k);
+            a4[0] = x.x; a4[1] = x.y; a4[2] = x.z; a4[3] = x.w; i4[0] = z.x; i4[1] = z.y; i4[2] = z.z; i4[3] = z.w;
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { a4[q] = k + q < bw ? ra_row[k + q] : 0.f; i4[q] = k + q < bw ? ri_row[k + q] : 0.f; }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (k + q < bw) {
+                ra = fmaf(a4[q], mine[k + q], ra);
+                ri = fmaf(i4[q], mine[k + q], ri);
+            }
+        }
+    }
+    const size_t at = (size_t)j * width + b * bw + o;
+    const float r = rg_sigmoid(ra + bias_a), i = rg_sigmoid(ri + bias_i);
+    const float log_a = -gain * r * sp;
+    a_out[at] = -expm1f(log_a);
+    drive_out[at] = sqrtf(-expm1f(2.0f * log_a)) * i * mine[o];
 }
 }  // namespace
 
@@ -104,6 +174,11 @@ DD_API int dd_recurrence_gates(const float* u, const float* wa, const float* ba,
     if (n_tokens <= 0) return 0;
     if (width <= 0 || blocks <= 0 || width % blocks) return dd_fail("dd_recurrence_gates: %d channels do not fall into %d equal parts", width, blocks);
     const int bw = width / blocks;
+    if (n_tokens <= RG_FEW && (size_t)n_tokens * bw * sizeof(float) <= 48 * 1024) {
+        dd_launch(recurrence_gates_few_kernel, dim3(dd_ceil_div(bw, RG_FEW_OUTS), blocks), dim3(32 * n_tokens), (size_t)n_tokens * bw * sizeof(float),
+                  (cudaStream_t)stream, u, wa, ba, wi, bi, lam, gain, a_out, drive_out, n_tokens, width, bw);
+        return dd_check_launch("dd_recurrence_gates");
+    }
     const dim3 grid(dd_ceil_div(n_tokens, RG_TOKENS), blocks, dd_ceil_div(bw, RG_OUTS));
     dd_launch(recurrence_gates_kernel, grid, dim3(RG_OUTS), 0, (cudaStream_t)stream, u, wa, ba, wi, bi, lam, gain, a_out, drive_out,
               n_tokens, width, bw);

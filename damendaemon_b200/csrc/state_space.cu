@@ -46,8 +46,12 @@ conv_channels_kernel(const T* __restrict__ in, int in_stride, const float* __res
 }
 
 constexpr int SS_THREADS = 128;
+constexpr int SS_TOKENS = 16;         // tokens staged together
 
-// LPC lanes share a column; each holds rows sub * 8 .. sub * 8 + 7 of it.
+// LPC lanes share a column; each holds rows sub * 8 .. sub * 8 + 7 of it. The tokens of an entry are staged SS_TOKENS at a
+// time in shared memory: B and C rows (padded with zeros to the rows the lanes hold), the block's columns of x, and the step
+// size and 1 - decay of every token, which 16 threads compute side by side so that the exponentials and the logarithm do
+// not lie on the chain from token to token. While a chunk is worked on, the next one is already on its way in registers.
 template <typename T, int LPC>
 __global__ void __launch_bounds__(SS_THREADS)
 state_space_scan_kernel(const float* __restrict__ xbc, int xbc_stride, const T* __restrict__ dt_in, int dt_stride,
@@ -55,39 +59,80 @@ state_space_scan_kernel(const float* __restrict__ xbc, int xbc_stride, const T* 
                         const int* __restrict__ entry_start, const int* __restrict__ entry_slot, float* __restrict__ state,
                         float* __restrict__ out, int H, int G, int N, int dv) {
     constexpr int NP = LPC * 8, COLS = SS_THREADS / LPC;
+    constexpr int ROW = 2 * NP + COLS;                                   // staged floats of one token: B, C, x
+    constexpr int PER_THREAD = (SS_TOKENS * ROW + SS_THREADS - 1) / SS_THREADS;
+    __shared__ __align__(16) float staged[SS_TOKENS * ROW];
+    __shared__ float steps[SS_TOKENS], fades[SS_TOKENS];
     dd_launch_dependents();
     const int e = blockIdx.z, h = blockIdx.y, g = h / (H / G);
-    const int col = blockIdx.x * COLS + threadIdx.x / LPC, sub = threadIdx.x % LPC;
+    const int col0 = blockIdx.x * COLS;
+    const int my_col = threadIdx.x / LPC, sub = threadIdx.x % LPC;
+    const int col = col0 + my_col;
     const bool live = col < dv;
     const int start = entry_start[e], end = entry_start[e + 1];
     float* sp = state + (((size_t)entry_slot[e] * H + h) * dv + (live ? col : 0)) * NP + sub * 8;
     const float rate = -expf(a_log[h]), bias = dt_bias[h], d_skip = skip[h];
     const int inner = H * dv;
-    const int b_at = inner + g * N + sub * 8, c_at = inner + G * N + g * N + sub * 8;
+    const int b_from = inner + g * N, c_from = inner + G * N + g * N, x_from = h * dv + col0;
     dd_grid_wait();
     float s[8];
     {
         const float4 a = *reinterpret_cast<const float4*>(sp), b = *reinterpret_cast<const float4*>(sp + 4);
         s[0] = a.x; s[1] = a.y; s[2] = a.z; s[3] = a.w; s[4] = b.x; s[5] = b.y; s[6] = b.z; s[7] = b.w;
     }
-    for (int t = start; t < end; ++t) {
-        const float* row = xbc + (size_t)t * xbc_stride;
-        const float dt = ss_softplus(dd_to_f32(dt_in[(size_t)t * dt_stride + h]) + bias);
-        const float fade = -expm1f(rate * dt);        // 1 - decay: a decay near one would lose its distance from one to rounding
-        const float x = live ? row[h * dv + col] : 0.f;
-        const float dtx = dt * x;
-        float y = 0.f;
+    float ahead[PER_THREAD], dt_ahead = 0.f;
+    // element i of a chunk: token i / ROW, then B rows [0, NP), C rows [NP, 2 NP), x columns [2 NP, ROW)
+    auto fetch = [&](int t0) {
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const int n = sub * 8 + r;
-            const float bn = n < N ? row[b_at + r] : 0.f;
-            const float cn = n < N ? row[c_at + r] : 0.f;
-            s[r] = fmaf(dtx, bn, fmaf(-fade, s[r], s[r]));
-            y = fmaf(s[r], cn, y);
+        for (int j = 0; j < PER_THREAD; ++j) {
+            const int i = threadIdx.x + j * SS_THREADS;
+            const int tok = i / ROW, r = i % ROW;
+            float v = 0.f;
+            if (i < SS_TOKENS * ROW && t0 + tok < end) {
+                const float* row = xbc + (size_t)(t0 + tok) * xbc_stride;
+                if (r < NP) { if (r < N) v = row[b_from + r]; }
+                else if (r < 2 * NP) { if (r - NP < N) v = row[c_from + r - NP]; }
+                else if (col0 + r - 2 * NP < dv) v = row[x_from + r - 2 * NP];
+            }
+            ahead[j] = v;
         }
+        if (threadIdx.x < SS_TOKENS && t0 + (int)threadIdx.x < end) dt_ahead = dd_to_f32(dt_in[(size_t)(t0 + threadIdx.x) * dt_stride + h]);
+    };
+    fetch(start);
+    for (int t0 = start; t0 < end; t0 += SS_TOKENS) {
+        __syncthreads();                                  // the chunk before has been read
 #pragma unroll
-        for (int o = LPC / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-        if (live && sub == 0) out[(size_t)t * inner + h * dv + col] = fmaf(d_skip, x, y);
+        for (int j = 0; j < PER_THREAD; ++j) {
+            const int i = threadIdx.x + j * SS_THREADS;
+            if (i < SS_TOKENS * ROW) staged[i] = ahead[j];
+        }
+        if (threadIdx.x < SS_TOKENS) {
+            const float dt = ss_softplus(dt_ahead + bias);
+            steps[threadIdx.x] = dt;
+            fades[threadIdx.x] = -expm1f(rate * dt);      // 1 - decay: a decay near one would lose its distance from one to rounding
+        }
+        __syncthreads();
+        if (t0 + SS_TOKENS < end) fetch(t0 + SS_TOKENS);
+        const int n = min(SS_TOKENS, end - t0);
+        for (int k = 0; k < n; ++k) {
+            const float* row = staged + k * ROW;
+            const float dt = steps[k], fade = fades[k];
+            const float x = row[2 * NP + my_col];
+            const float dtx = dt * x;
+            const float4 b0 = *reinterpret_cast<const float4*>(row + sub * 8), b1 = *reinterpret_cast<const float4*>(row + sub * 8 + 4);
+            const float4 c0 = *reinterpret_cast<const float4*>(row + NP + sub * 8), c1 = *reinterpret_cast<const float4*>(row + NP + sub * 8 + 4);
+            const float bn[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const float cn[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            float y = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                s[r] = fmaf(dtx, bn[r], fmaf(-fade, s[r], s[r]));
+                y = fmaf(s[r], cn[r], y);
+            }
+#pragma unroll
+            for (int o = LPC / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (live && sub == 0) out[(size_t)(t0 + k) * inner + h * dv + col] = fmaf(d_skip, x, y);
+        }
     }
     if (live) {
         *reinterpret_cast<float4*>(sp) = make_float4(s[0], s[1], s[2], s[3]);
@@ -95,31 +140,89 @@ state_space_scan_kernel(const float* __restrict__ xbc, int xbc_stride, const T* 
     }
 }
 
+// A block owns a stretch of one token. A thread keeps up to GN_KEEP gated values in registers between the sum of squares and
+// the scaling; a stretch longer than the block holds that way is gated again in the second pass (the same instructions).
+constexpr int GN_KEEP = 8;
+
+// Entries of one token each (a decode step): nothing to stage; a thread reads its rows of B and C and its column of x
+// directly. The arithmetic of a token is that of the staged kernel, instruction for instruction.
+template <typename T, int LPC>
+__global__ void __launch_bounds__(SS_THREADS)
+state_space_single_kernel(const float* __restrict__ xbc, int xbc_stride, const T* __restrict__ dt_in, int dt_stride,
+                          const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ skip,
+                          const int* __restrict__ entry_start, const int* __restrict__ entry_slot, float* __restrict__ state,
+                          float* __restrict__ out, int H, int G, int N, int dv) {
+    constexpr int NP = LPC * 8, COLS = SS_THREADS / LPC;
+    dd_launch_dependents();
+    const int e = blockIdx.z, h = blockIdx.y, g = h / (H / G);
+    const int col = blockIdx.x * COLS + threadIdx.x / LPC, sub = threadIdx.x % LPC;
+    const bool live = col < dv;
+    const int t = entry_start[e];
+    float* sp = state + (((size_t)entry_slot[e] * H + h) * dv + (live ? col : 0)) * NP + sub * 8;
+    const float rate = -expf(a_log[h]), bias = dt_bias[h], d_skip = skip[h];
+    const int inner = H * dv;
+    dd_grid_wait();
+    const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+    float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const float* row = xbc + (size_t)t * xbc_stride;
+    const float dt = ss_softplus(dd_to_f32(dt_in[(size_t)t * dt_stride + h]) + bias);
+    const float fade = -expm1f(rate * dt);
+    const float x = live ? row[h * dv + col] : 0.f;
+    const float dtx = dt * x;
+    float y = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const int n = sub * 8 + r;
+        const float bn = n < N ? row[inner + g * N + n] : 0.f;
+        const float cn = n < N ? row[inner + G * N + g * N + n] : 0.f;
+        s[r] = fmaf(dtx, bn, fmaf(-fade, s[r], s[r]));
+        y = fmaf(s[r], cn, y);
+    }
+#pragma unroll
+    for (int o = LPC / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+    if (live) {
+        if (sub == 0) out[(size_t)t * inner + h * dv + col] = fmaf(d_skip, x, y);
+        *reinterpret_cast<float4*>(sp) = make_float4(s[0], s[1], s[2], s[3]);
+        *reinterpret_cast<float4*>(sp + 4) = make_float4(s[4], s[5], s[6], s[7]);
+    }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, int z_stride, const float* __restrict__ w, float eps,
                         T* __restrict__ out, int out_stride, int groups, int inner) {
-    __shared__ float scratch[4];
+    __shared__ float scratch[8];
     dd_launch_dependents();
     dd_grid_wait();
     const int t = blockIdx.x, g = blockIdx.y, size = inner / groups;
     const float* yr = y + (size_t)t * inner + g * size;
     const T* zr = z + (size_t)t * z_stride + g * size;
-    float sum = 0.f;
-    for (int c = threadIdx.x; c < size; c += 128) {
+    auto gated = [&](int c) {
         const float gate = dd_to_f32(zr[c]);
-        const float v = yr[c] * (gate / (1.0f + expf(-gate)));
-        sum = fmaf(v, v, sum);
+        return yr[c] * (gate / (1.0f + expf(-gate)));
+    };
+    float kept[GN_KEEP];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < GN_KEEP; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        kept[j] = c < size ? gated(c) : 0.f;
+        sum = fmaf(kept[j], kept[j], sum);
     }
+    for (int c = threadIdx.x + GN_KEEP * blockDim.x; c < size; c += blockDim.x) { const float v = gated(c); sum = fmaf(v, v, sum); }
     sum = dd_warp_sum(sum);
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = sum;
     __syncthreads();
-    const float r = rsqrtf((scratch[0] + scratch[1] + scratch[2] + scratch[3]) / (float)size + eps);
-    for (int c = threadIdx.x; c < size; c += 128) {
-        const float gate = dd_to_f32(zr[c]);
-        const float v = yr[c] * (gate / (1.0f + expf(-gate)));
-        out[(size_t)t * out_stride + g * size + c] = dd_from_f32<T>(v * r * w[g * size + c]);
+    float total = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) total += scratch[i];
+    const float r = rsqrtf(total / (float)size + eps);
+    T* o = out + (size_t)t * out_stride + g * size;
+#pragma unroll
+    for (int j = 0; j < GN_KEEP; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < size) o[c] = dd_from_f32<T>(kept[j] * r * w[g * size + c]);
     }
+    for (int c = threadIdx.x + GN_KEEP * blockDim.x; c < size; c += blockDim.x) o[c] = dd_from_f32<T>(gated(c) * r * w[g * size + c]);
 }
 
 int lanes_per_column(int n) {
@@ -129,11 +232,13 @@ int lanes_per_column(int n) {
 }
 
 template <typename T>
-int launch_scan(int lpc, dim3 grid, cudaStream_t s, const float* xbc, int xbc_stride, const T* dt_in, int dt_stride,
+int launch_scan(bool single, int lpc, dim3 grid, cudaStream_t s, const float* xbc, int xbc_stride, const T* dt_in, int dt_stride,
                 const float* dt_bias, const float* a_log, const float* skip, const int* entry_start, const int* entry_slot,
                 float* state, float* out, int H, int G, int N, int dv) {
-#define SS_CASE(L) case L: dd_launch(state_space_scan_kernel<T, L>, grid, dim3(SS_THREADS), 0, s, xbc, xbc_stride, dt_in, dt_stride, \
-                                     dt_bias, a_log, skip, entry_start, entry_slot, state, out, H, G, N, dv); break;
+#define SS_CASE(L) case L: if (single) dd_launch(state_space_single_kernel<T, L>, grid, dim3(SS_THREADS), 0, s, xbc, xbc_stride, dt_in, \
+                                                 dt_stride, dt_bias, a_log, skip, entry_start, entry_slot, state, out, H, G, N, dv); \
+                   else dd_launch(state_space_scan_kernel<T, L>, grid, dim3(SS_THREADS), 0, s, xbc, xbc_stride, dt_in, dt_stride, \
+                                  dt_bias, a_log, skip, entry_start, entry_slot, state, out, H, G, N, dv); break;
     switch (lpc) {
         SS_CASE(1) SS_CASE(2) SS_CASE(4) SS_CASE(8) SS_CASE(16) SS_CASE(32)
         default: return dd_fail("dd_state_space_scan: a state of %d rows is not supported (at most 256)", N);
@@ -168,9 +273,10 @@ DD_API int dd_conv_channels(const void* in, int in_stride, const float* taps_w, 
 
 // xbc: float32 [N, H * dv + 2 * G * n_state] rows ([x | B | C], after the convolution and its activation); dt_in: [N, H] row
 // view in `dtype`; state: float32 [slots, H, dv, dd_state_space_rows(n_state)], read and written; out: float32 [N, H * dv].
+// n_tokens == n_entries (every entry brings one token) takes the kernel without staging.
 DD_API int dd_state_space_scan(const float* xbc, int xbc_stride, const void* dt_in, int dt_stride, const float* dt_bias,
                                const float* a_log, const float* skip, const int* entry_start, const int* entry_slot, int n_entries,
-                               float* state, float* out, int H, int G, int n_state, int dv, int dtype, void* stream) {
+                               float* state, float* out, int H, int G, int n_state, int dv, int dtype, void* stream, int n_tokens) {
     if (n_entries <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || n_state <= 0 || n_state > 256 || dv <= 0)
         return dd_fail("dd_state_space_scan: %d heads in %d groups with a state of %d by %d are not supported", H, G, n_state, dv);
@@ -178,10 +284,10 @@ DD_API int dd_state_space_scan(const float* xbc, int xbc_stride, const void* dt_
     const int lpc = lanes_per_column(n_state);
     const dim3 grid(dd_ceil_div(dv, SS_THREADS / lpc), H, n_entries);
     if (dtype == DD_F32)
-        return launch_scan<float>(lpc, grid, s, xbc, xbc_stride, (const float*)dt_in, dt_stride, dt_bias, a_log, skip, entry_start,
+        return launch_scan<float>(n_tokens == n_entries, lpc, grid, s, xbc, xbc_stride, (const float*)dt_in, dt_stride, dt_bias, a_log, skip, entry_start,
                                   entry_slot, state, out, H, G, n_state, dv);
     if (dtype == DD_BF16)
-        return launch_scan<__nv_bfloat16>(lpc, grid, s, xbc, xbc_stride, (const __nv_bfloat16*)dt_in, dt_stride, dt_bias, a_log, skip,
+        return launch_scan<__nv_bfloat16>(n_tokens == n_entries, lpc, grid, s, xbc, xbc_stride, (const __nv_bfloat16*)dt_in, dt_stride, dt_bias, a_log, skip,
                                           entry_start, entry_slot, state, out, H, G, n_state, dv);
     return dd_fail("dd_state_space_scan: unknown dtype %d", dtype);
 }
@@ -193,11 +299,13 @@ DD_API int dd_gated_group_norm(const float* y, const void* z, int z_stride, cons
     if (groups <= 0 || inner <= 0 || inner % groups) return dd_fail("dd_gated_group_norm: %d does not fall into %d equal parts", inner, groups);
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(n_tokens, groups);
+    const int size = inner / groups;
+    const int threads = size > 1024 ? 256 : (size > 256 ? 128 : (size > 64 ? 64 : 32));
     if (dtype == DD_F32)
-        dd_launch(gated_group_norm_kernel<float>, grid, dim3(128), 0, s, y, (const float*)z, z_stride, w, eps, (float*)out, out_stride,
+        dd_launch(gated_group_norm_kernel<float>, grid, dim3(threads), 0, s, y, (const float*)z, z_stride, w, eps, (float*)out, out_stride,
                   groups, inner);
     else if (dtype == DD_BF16)
-        dd_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, y, (const __nv_bfloat16*)z, z_stride, w, eps,
+        dd_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, y, (const __nv_bfloat16*)z, z_stride, w, eps,
                   (__nv_bfloat16*)out, out_stride, groups, inner);
     else
         return dd_fail("dd_gated_group_norm: unknown dtype %d", dtype);

@@ -78,60 +78,115 @@ norm_pair_add_kernel(float* __restrict__ x, const float* __restrict__ left, cons
         x[at + c] += half * (left[at + c] * rl * wl[c] + right[at + c] * rr * wr[c]);
 }
 
-template <typename T>
+// A block owns a token. Its cosines and sines are computed once (before the wait for the kernel before: they depend on the
+// position only); the token's queries and keys are brought into shared memory as float32 in one pass of 16-byte loads that
+// also sums their squares; pairs are rotated there, and one pass of 16-byte stores writes the row back. STAGED false: rows
+// that do not fit shared memory, or are not 16-byte aligned, are normed and rotated in place from global memory.
+template <typename T, bool STAGED>
 __global__ void __launch_bounds__(256)
 wide_norm_rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __restrict__ positions,
                         const float* __restrict__ freqs, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
                         int q_heads, int k_heads, int d, int n_pairs, int interleaved) {
-    __shared__ float scratch[8];
+    extern __shared__ __align__(16) float wn_shared[];
+    __shared__ float sums[2][8];
+    constexpr int PIECE = 16 / sizeof(T);
     dd_launch_dependents();
-    dd_grid_wait();
     const int t = blockIdx.x;
-    const float p = (float)positions[t];
-    for (int which = 0; which < 2; ++which) {
-        T* row = (which ? k : q);
-        const int heads = which ? k_heads : q_heads;
-        const float* w = which ? kw : qw;
-        if (row == nullptr || heads == 0) continue;
-        row += (size_t)t * stride;
-        const int total = heads * d;
-        float r = 1.0f;
-        if (w != nullptr) {
+    const int nq = q_heads * d, nk = k ? k_heads * d : 0;
+    float* cosines = wn_shared;
+    float* sines = wn_shared + n_pairs;
+    float* row = wn_shared + 2 * n_pairs + ((-2 * n_pairs) & 3);          // [nq + nk], 16-byte aligned
+    {
+        const float p = (float)positions[t];
+        for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) sincosf(p * freqs[i], &sines[i], &cosines[i]);
+    }
+    dd_grid_wait();
+    T* qr = q + (size_t)t * stride;
+    T* kr = k ? k + (size_t)t * stride : nullptr;
+    float sq = 0.f, sk = 0.f;
+    if (STAGED) {
+        for (int c = threadIdx.x * PIECE; c < nq + nk; c += blockDim.x * PIECE) {
+            const bool is_k = c >= nq;
+            const T* src = is_k ? kr + (c - nq) : qr + c;
+            T piece[PIECE];
+            *reinterpret_cast<uint4*>(piece) = *reinterpret_cast<const uint4*>(src);
             float s = 0.f;
-            for (int c = threadIdx.x; c < total; c += blockDim.x) { const float v = dd_to_f32(row[c]); s = fmaf(v, v, s); }
-            r = rsqrtf(block_sum(s, scratch) / (float)total + eps);
+#pragma unroll
+            for (int j = 0; j < PIECE; ++j) { const float v = dd_to_f32(piece[j]); row[c + j] = v; s = fmaf(v, v, s); }
+            if (is_k) sk += s; else sq += s;
         }
-        // a thread owns whole pairs (and single elements of the unrotated rest), so nothing is read after it was written
-        const int per_head = d - n_pairs;           // items of a head: n_pairs pairs, then d - 2 n_pairs single elements
-        for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
-            const int h = item / per_head, i = item % per_head;
-            if (i < n_pairs) {
-                const int a = h * d + (interleaved ? 2 * i : i), b = h * d + (interleaved ? 2 * i + 1 : i + n_pairs);
-                float u = dd_to_f32(row[a]) * r, v = dd_to_f32(row[b]) * r;
-                if (w) { u *= w[a]; v *= w[b]; }
-                const float angle = p * freqs[i];
-                const float c = cosf(angle), s = sinf(angle);
-                row[a] = dd_from_f32<T>(u * c - v * s);
-                row[b] = dd_from_f32<T>(v * c + u * s);
-            } else {
-                const int a = h * d + n_pairs + i;
-                float u = dd_to_f32(row[a]) * r;
-                if (w) u *= w[a];
-                row[a] = dd_from_f32<T>(u);
-            }
+    } else {
+        for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = dd_to_f32(qr[c]); sq = fmaf(v, v, sq); }
+        for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = dd_to_f32(kr[c]); sk = fmaf(v, v, sk); }
+    }
+    sq = dd_warp_sum(sq);
+    sk = dd_warp_sum(sk);
+    if ((threadIdx.x & 31) == 0) { sums[0][threadIdx.x >> 5] = sq; sums[1][threadIdx.x >> 5] = sk; }
+    __syncthreads();
+    sq = sk = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) { sq += sums[0][i]; sk += sums[1][i]; }      // every thread adds in one order
+    const float rq = qw ? rsqrtf(sq / (float)nq + eps) : 1.0f;
+    const float rk = (kw && nk) ? rsqrtf(sk / (float)nk + eps) : 1.0f;
+    // a thread owns whole pairs (and single elements of the unrotated rest), so nothing is read after it was written
+    const int per_head = d - n_pairs;               // items of a head: n_pairs pairs, then d - 2 n_pairs single elements
+    const int q_items = q_heads * per_head, items = q_items + (k ? k_heads * per_head : 0);
+    for (int item = threadIdx.x; item < items; item += blockDim.x) {
+        const bool is_k = item >= q_items;
+        const int local = is_k ? item - q_items : item;
+        const int h = local / per_head, i = local % per_head;
+        const float* w = is_k ? kw : qw;
+        const float r = is_k ? rk : rq;
+        const int base = h * d;
+        const int off = is_k ? nq : 0;
+        T* dst = is_k ? kr : qr;
+        if (i < n_pairs) {
+            const int a = base + (interleaved ? 2 * i : i), b = base + (interleaved ? 2 * i + 1 : i + n_pairs);
+            float u = (STAGED ? row[off + a] : dd_to_f32(dst[a])) * r, v = (STAGED ? row[off + b] : dd_to_f32(dst[b])) * r;
+            if (w) { u *= w[a]; v *= w[b]; }
+            const float c = cosines[i], sn = sines[i];
+            const float ru = u * c - v * sn, rv = v * c + u * sn;
+            if (STAGED) { row[off + a] = ru; row[off + b] = rv; } else { dst[a] = dd_from_f32<T>(ru); dst[b] = dd_from_f32<T>(rv); }
+        } else {
+            const int a = base + n_pairs + i;
+            float u = (STAGED ? row[off + a] : dd_to_f32(dst[a])) * r;
+            if (w) u *= w[a];
+            if (STAGED) row[off + a] = u; else dst[a] = dd_from_f32<T>(u);
         }
+    }
+    if (!STAGED) return;
+    __syncthreads();
+    for (int c = threadIdx.x * PIECE; c < nq + nk; c += blockDim.x * PIECE) {
+        T* dst = c >= nq ? kr + (c - nq) : qr + c;
+        T piece[PIECE];
+#pragma unroll
+        for (int j = 0; j < PIECE; ++j) piece[j] = dd_from_f32<T>(row[c + j]);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(piece);
     }
 }
 
-template <typename T>
+// An item is a 16-byte piece of a row (WIDE) or one element; the grid covers all items of all rows.
+template <typename T, bool WIDE>
 __global__ void __launch_bounds__(256)
-sigmoid_gate_kernel(T* __restrict__ x, int x_stride, const T* __restrict__ gate, int gate_stride, int width) {
+sigmoid_gate_kernel(T* __restrict__ x, int x_stride, const T* __restrict__ gate, int gate_stride, int rows, int width) {
+    constexpr int PIECE = WIDE ? 16 / sizeof(T) : 1;
     dd_launch_dependents();
     dd_grid_wait();
-    T* xr = x + (size_t)blockIdx.x * x_stride;
-    const T* gr = gate + (size_t)blockIdx.x * gate_stride;
-    for (int c = threadIdx.x; c < width; c += blockDim.x)
-        xr[c] = dd_from_f32<T>(dd_to_f32(xr[c]) / (1.0f + expf(-dd_to_f32(gr[c]))));
+    const int per_row = width / PIECE;
+    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (long long)rows * per_row) return;
+    const int r = (int)(item / per_row), c = (int)(item % per_row) * PIECE;
+    T* xp = x + (size_t)r * x_stride + c;
+    const T* gp = gate + (size_t)r * gate_stride + c;
+    if (WIDE) {
+        T xs[PIECE], gs[PIECE];
+        *reinterpret_cast<uint4*>(xs) = *reinterpret_cast<const uint4*>(xp);
+        *reinterpret_cast<uint4*>(gs) = *reinterpret_cast<const uint4*>(gp);
+#pragma unroll
+        for (int j = 0; j < PIECE; ++j) xs[j] = dd_from_f32<T>(dd_to_f32(xs[j]) / (1.0f + expf(-dd_to_f32(gs[j]))));
+        *reinterpret_cast<uint4*>(xp) = *reinterpret_cast<const uint4*>(xs);
+    } else {
+        *xp = dd_from_f32<T>(dd_to_f32(*xp) / (1.0f + expf(-dd_to_f32(*gp))));
+    }
 }
 
 __global__ void __launch_bounds__(256) tanh_cap_kernel(float* __restrict__ x, long long n, float cap) {
@@ -179,28 +234,36 @@ DD_API int dd_wide_norm_rotary(void* q, void* k, int stride, const int* position
     if (n_tokens <= 0) return 0;
     if (d <= 0 || n_pairs < 0 || 2 * n_pairs > d) return dd_fail("dd_wide_norm_rotary: %d pairs do not fit a head of %d", n_pairs, d);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == DD_F32)
-        dd_launch(wide_norm_rotary_kernel<float>, dim3(n_tokens), dim3(256), 0, s, (float*)q, (float*)k, stride, positions, freqs,
-                  qw, kw, eps, q_heads, k_heads, d, n_pairs, interleaved);
-    else if (dtype == DD_BF16)
-        dd_launch(wide_norm_rotary_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, s, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-                  stride, positions, freqs, qw, kw, eps, q_heads, k_heads, d, n_pairs, interleaved);
-    else
-        return dd_fail("dd_wide_norm_rotary: unknown dtype %d", dtype);
+    const int nq = q_heads * d, nk = k ? k_heads * d : 0;
+    const int elem = dtype == DD_F32 ? 4 : 2, piece = 16 / elem;
+    const size_t table = (size_t)(2 * n_pairs + 3) * sizeof(float);
+    // staged: every piece of 16 bytes lies inside q or inside k and is aligned, and the row fits shared memory
+    const bool staged = nq % piece == 0 && nk % piece == 0 && stride % piece == 0 && (uintptr_t)q % 16 == 0 &&
+                        (k == nullptr || (uintptr_t)k % 16 == 0) && table + (size_t)(nq + nk) * 4 <= 40 * 1024;
+    const size_t smem = table + (staged ? (size_t)(nq + nk) * 4 : 0);
+    const int threads = (nq + nk) >= 2048 ? 256 : 128;
+#define WN_LAUNCH(T, STAGED) dd_launch(wide_norm_rotary_kernel<T, STAGED>, dim3(n_tokens), dim3(threads), smem, s, (T*)q, (T*)k, stride, \
+                                       positions, freqs, qw, kw, eps, q_heads, k_heads, d, n_pairs, interleaved)
+    if (dtype == DD_F32) { if (staged) WN_LAUNCH(float, true); else WN_LAUNCH(float, false); }
+    else if (dtype == DD_BF16) { if (staged) WN_LAUNCH(__nv_bfloat16, true); else WN_LAUNCH(__nv_bfloat16, false); }
+    else return dd_fail("dd_wide_norm_rotary: unknown dtype %d", dtype);
+#undef WN_LAUNCH
     return dd_check_launch("dd_wide_norm_rotary");
 }
 
 DD_API int dd_sigmoid_gate(void* x, int x_stride, const void* gate, int gate_stride, int rows, int width, int dtype, void* stream) {
     if (rows <= 0 || width <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = width >= 1024 ? 256 : 128;
-    if (dtype == DD_F32)
-        dd_launch(sigmoid_gate_kernel<float>, dim3(rows), dim3(threads), 0, s, (float*)x, x_stride, (const float*)gate, gate_stride, width);
-    else if (dtype == DD_BF16)
-        dd_launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, s, (__nv_bfloat16*)x, x_stride,
-                  (const __nv_bfloat16*)gate, gate_stride, width);
-    else
-        return dd_fail("dd_sigmoid_gate: unknown dtype %d", dtype);
+    const int elem = dtype == DD_F32 ? 4 : 2, piece = 16 / elem;
+    const bool wide = width % piece == 0 && x_stride % piece == 0 && gate_stride % piece == 0 && (uintptr_t)x % 16 == 0 &&
+                      (uintptr_t)gate % 16 == 0;
+    const long long items = (long long)rows * (wide ? width / piece : width);
+    const dim3 grid(dd_ceil_div(items, 128));
+#define SG_LAUNCH(T, WIDE) dd_launch(sigmoid_gate_kernel<T, WIDE>, grid, dim3(128), 0, s, (T*)x, x_stride, (const T*)gate, gate_stride, rows, width)
+    if (dtype == DD_F32) { if (wide) SG_LAUNCH(float, true); else SG_LAUNCH(float, false); }
+    else if (dtype == DD_BF16) { if (wide) SG_LAUNCH(__nv_bfloat16, true); else SG_LAUNCH(__nv_bfloat16, false); }
+    else return dd_fail("dd_sigmoid_gate: unknown dtype %d", dtype);
+#undef SG_LAUNCH
     return dd_check_launch("dd_sigmoid_gate");
 }
 

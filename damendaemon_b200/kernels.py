@@ -75,7 +75,7 @@ _SIGNATURES = {
         "dd_conv_channels": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                              _c_int, _c_int, _c_int, _c_int, _c_void],
         "dd_state_space_scan": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void]
-                               + [_c_int] * 5 + [_c_void],
+                               + [_c_int] * 5 + [_c_void, _c_int],
         "dd_gated_group_norm": [_c_void, _c_void, _c_int, _c_void, _c_float, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
         "dd_recurrence_gates": [_c_void] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
         "dd_linear_scan": [_c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_int,
@@ -103,6 +103,8 @@ _SIGNATURES = {
         "dd_attention_prefill_tcgen05_supported": [_c_int] * 5,
         "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
                                         + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int],
+        "dd_attention_prefill_tcgen05_sink": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
+                                             + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void],
         "dd_attention_decode_pages_supported": [_c_int] * 5,
         "dd_attention_decode_pages_splits": [_c_int] * 5,
         "dd_attention_decode_pages": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
@@ -440,7 +442,7 @@ def state_space_scan(xbc, dt, dt_bias, a_log, skip, entry_start, entry_slot, sta
         out = torch.empty((n, inner), dtype=torch.float32, device=xbc.device)
     _call(library("core"), "dd_state_space_scan", _ptr(xbc), xbc.stride(0), _ptr(dt, "dt"), dt.stride(0), _ptr(dt_bias), _ptr(a_log),
           _ptr(skip), _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_slot, "entry_slot", torch.int32), entry_slot.numel(),
-          _ptr(state), _ptr(out), heads, groups, n_state, value_dim, _dt(dt.dtype), _stream())
+          _ptr(state), _ptr(out), heads, groups, n_state, value_dim, _dt(dt.dtype), _stream(), n)
     return out
 
 
@@ -1222,12 +1224,18 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
     in this step from there, in one piece per block instead of page by page. store_new: the tcgen05 kernel writes
     k_new/v_new into the cache itself (no kv_store before it); only for steps whose entries all start at a position
     that is a multiple of ATTENTION_PREFILL_TCGEN05_KEY_BLOCK (an entry that does not sets error bit 2).
-    chunk, gate, keep_first, softcap, sink: as attention_rows; the last three, and exact_weights (the softmax weights
-    meet the values as two bfloat16 terms instead of one rounded to bfloat16), only with kernel 'mma'."""
+    chunk, gate, keep_first, softcap, sink: as attention_rows; keep_first, softcap and exact_weights (the softmax weights
+    meet the values as two bfloat16 terms instead of one rounded to bfloat16) only with kernel 'mma'; a sink alone also with
+    'tcgen05'."""
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n, n_entries = q.shape[0], entry_pos0.numel()
     more = ()
-    if keep_first or softcap or sink is not None or exact_weights:
+    if kernel == "tcgen05" and sink is not None and not (keep_first or softcap or exact_weights):
+        # the tcgen05 kernel takes a sink (one more term in a row's denominator), none of the other three
+        if sink.numel() != n_heads or sink.dtype != torch.float32 or not sink.is_contiguous():
+            raise KernelError("attention: the sink must be float32 [heads]")
+        more, kernel = (_ptr(sink, "sink"),), "tcgen05_sink"
+    elif keep_first or softcap or sink is not None or exact_weights:
         if kernel != "mma":
             raise KernelError("attention_prefill: kept first keys, capped scores, a sink and exact weights need the kernel 'mma'")
         if sink is not None and (sink.numel() != n_heads or sink.dtype != torch.float32 or not sink.is_contiguous()):
@@ -1238,17 +1246,18 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
         raise KernelError("attention_prefill: q or the entry arrays do not fit the cache")
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=q.dtype, device=q.device)
-    if kernel not in ("mma", "tcgen05"):
+    if kernel not in ("mma", "tcgen05", "tcgen05_sink"):
         raise KernelError(f"attention_prefill: unknown kernel {kernel!r}")
+    tensor_memory = kernel != "mma"
     if (k_new is None) != (v_new is None) or (k_new is not None and (
-            kernel != "tcgen05" or k_new.stride(0) != q.stride(0) or v_new.stride(0) != q.stride(0) or k_new.stride(1) != 1
+            not tensor_memory or k_new.stride(0) != q.stride(0) or v_new.stride(0) != q.stride(0) or k_new.stride(1) != 1
             or v_new.stride(1) != 1 or k_new.dtype != q.dtype or v_new.dtype != q.dtype
             or k_new.shape != (n, kv_heads * head_dim) or v_new.shape != k_new.shape)):
         raise KernelError("attention_prefill: k_new and v_new come together, as row views like q, for the tcgen05 kernel")
     if store_new and k_new is None:
         raise KernelError("attention_prefill: store_new needs k_new and v_new")
-    new_rows = (_ptr(k_new, "k_new"), _ptr(v_new, "v_new"), int(bool(store_new))) if kernel == "tcgen05" else ()
-    _call(library("tensor"), "dd_attention_prefill" + ("_tcgen05" if kernel == "tcgen05" else "_sinks" if more else ""), _ptr(q, "q"), q.stride(0), *new_rows,
+    new_rows = (_ptr(k_new, "k_new"), _ptr(v_new, "v_new"), int(bool(store_new))) if tensor_memory else ()
+    _call(library("tensor"), "dd_attention_prefill" + ("_" + kernel if tensor_memory else "_sinks" if more else ""), _ptr(q, "q"), q.stride(0), *new_rows,
           _ptr(cache, "cache"),
           _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_pos0, "entry_pos0", torch.int32), n_entries, n,
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),

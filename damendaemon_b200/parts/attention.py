@@ -102,8 +102,8 @@ class Attention(Mixer):
         # what the attention kernels are told beside heads, scale and window
         self.mask = dict(chunk=spec.chunk, value_dim=None if plain else self.value_dim, keep_first=spec.keep_first,
                          softcap=spec.softcap, sink=self.sink, exact_weights=spec.exact_weights)
-        # (the tcgen05 prompt kernel takes none of these)
-        plain = plain and not spec.keep_first and not spec.softcap and self.sink is None and not spec.exact_weights
+        # (the tcgen05 prompt kernel takes a sink, none of the others)
+        plain = plain and not spec.keep_first and not spec.softcap and not spec.exact_weights
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"{spec.n_heads} heads cannot share {spec.n_kv_heads} key/value heads")
         # where this mixer likes a prompt to be cut: the key block of its prompt kernel, if that kernel takes its sizes

@@ -77,6 +77,8 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
     fast = runtime.attention != "rows"
     masked = dict(chunk=chunk, gate=gate)      # every kernel takes the chunked mask and the gate on its output
     tensor = fast and runtime.attention != "mma" and not special
+    # a sink alone (no kept first keys, no cap, no weights in two terms) the tcgen05 prompt kernel takes as well
+    sink_only = sink is not None and not (keep_first or softcap or exact_weights)
     def wants_pages(n_tokens):
         pairs = n_tokens * n_heads
         return pairs >= tune.pages_from_pairs or pairs * ctx.split_context >= tune.pages_from_pair_keys
@@ -93,7 +95,7 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         splits = ctx.key_splits(n_heads, keys_per_block=tune.row_keys_per_block, blocks_per_sm=tune.row_blocks_per_sm)
         return kernels.attention_decode(q, kv, None, ctx.positions, table, n_heads, scale, window,
                                         n_splits=splits, k_new=k_new, v_new=v_new, **masked, **exact)
-    tcgen05 = not ctx.decode_only and tensor and \
+    tcgen05 = not ctx.decode_only and (tensor or (sink_only and fast and runtime.attention != "mma")) and \
         kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, q.dtype)
     mma = not tcgen05 and not ctx.decode_only and fast and kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype)
     # A step that mixes portions with single tokens: the single tokens come first (ctx.n_single) and go to a decode
@@ -125,7 +127,7 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         kernels.kv_store(k[n1:], v[n1:], ctx.token_entry[n1:], ctx.positions[n1:], table, kv)
     if tcgen05:
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
-                                         out=out, kernel="tcgen05", k_new=k_new, v_new=v_new, store_new=fused_store, **masked)
+                                         out=out, kernel="tcgen05", k_new=k_new, v_new=v_new, store_new=fused_store, sink=sink, **masked)
     if mma:
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
                                          out=out, **masked, **exact)

@@ -370,3 +370,41 @@ def test_a_marked_key_at_every_edge_of_the_window_with_the_unit_term(dk, dv, win
     for r in rows:
         one = kernels.attention_rows(qd[r:r + 1], cache, ent[:1], pos.new_tensor([r]), table, n_splits=3, **common).cpu().double()
         assert torch.allclose(one, want[r:r + 1], atol=2e-4), r
+
+
+@pytest.mark.parametrize("G, window, sink_value", [(4, 100, 0.0), (2, None, 0.0), (4, 33, 1.5), (1, 300, -2.0)])
+def test_the_tcgen05_prompt_kernel_with_a_term_in_the_denominator(G, window, sink_value):
+    """Heads of 64 in bfloat16: a portion that starts in the middle of a prompt (and of a key block), through the tcgen05
+    prompt kernel with a sink, against the plain attention with that term in the denominator (one for a sink of 0); queries
+    whose window holds one key only lose most of their weight to the term."""
+    from damendaemon_b200 import kernels
+    H, d, T, page = 4, 64, 333, 16
+    if not kernels.attention_prefill_tcgen05_supported(H, G, d, page, torch.bfloat16):
+        pytest.skip("sizes the tcgen05 prompt kernel does not take")
+    r = lambda t: t.bfloat16().double()
+    q, k, v = randn(T, H, d, seed=1) * 0.4, randn(T, G, d, seed=2) * 0.4, randn(T, G, d, seed=3)
+    see = plain.visible(T, window)
+    # the plain attention's unit term is exp(0); a sink s is the same as scores shifted by -s with a unit term: by hand
+    scores = torch.einsum("thd,shd->hts", r(q), r(k)[:, torch.arange(H) // (H // G)]) * 0.125
+    scores = scores.masked_fill(~see[None], float("-inf"))
+    e = torch.exp(scores)
+    weights = e / (e.sum(-1, keepdim=True) + math.exp(sink_value))
+    want = torch.einsum("hts,shd->thd", weights, r(v)[:, torch.arange(H) // (H // G)]).reshape(T, -1)
+    if sink_value == 0.0:
+        assert torch.allclose(want, plain.attend(r(q), r(k), r(v), 0.125, see, True), atol=1e-12)
+    cache, table, _ = _paged(k.bfloat16(), v.bfloat16(), page, 7)
+    sink = torch.full((H,), sink_value, device=DEV)
+    first = 77
+    start = torch.tensor([0, T - first], dtype=torch.int32, device=DEV)
+    pos0 = torch.tensor([first], dtype=torch.int32, device=DEV)
+    qd = q[first:].reshape(T - first, -1).bfloat16().to(DEV)
+    got = kernels.attention_prefill(qd, cache, start, pos0, table, H, 0.125, window, kernel="tcgen05", sink=sink).cpu().double()
+    assert kernels.read_error_flag(DEV) == 0
+    assert (got - want[first:]).abs().max() < 0.03
+    general = kernels.attention_rows(qd, cache, torch.zeros(T - first, dtype=torch.int32, device=DEV),
+                                     torch.arange(first, T, dtype=torch.int32, device=DEV), table, H, 0.125, window, sink=sink).cpu().double()
+    assert (got - general).abs().max() < 0.03
+    if (window or T) < 50 or sink_value > 1.0:
+        # without the term the rows differ where it is a good part of the denominator: it is not idle
+        bare = kernels.attention_prefill(qd, cache, start, pos0, table, H, 0.125, window, kernel="tcgen05").cpu().double()
+        assert (bare - got).abs().max() > 0.05
