@@ -117,10 +117,12 @@ linear_scan_kernel(const float* __restrict__ a, const float* __restrict__ drive,
     *sp = s;
 }
 
-// A step of few tokens: a warp owns one token and 32 output channels of one part, a lane one channel, whose two weight rows it
-// streams in 16-byte pieces (the warps of a block read the same rows, from L1 after the first); the part's inputs of all the
-// step's tokens lie in shared memory. The sums run over the input channels in ascending order, the same multiply-adds in the
-// same order as in the tiled kernel, so a token's gates do not depend on which kernel computed them.
+// A step of few tokens: a block owns 32 output channels of one part and all the step's tokens, a warp one token, a lane one
+// channel. The part's inputs of all tokens lie in shared memory; the two weight matrices' rows of the block's channels pass
+// through shared memory 32 input channels at a time, each row's stretch read by one warp in one piece (a lane that streamed
+// its own row from global memory would touch 32 lines an instruction). The sums run over the input channels in ascending
+// order, the same multiply-adds in the same order as in the tiled kernel, so a token's gates do not depend on which kernel
+// computed them.
 constexpr int RG_FEW = 16, RG_FEW_OUTS = 32;
 
 __global__ void __launch_bounds__(RG_FEW * RG_FEW_OUTS)
@@ -128,37 +130,39 @@ recurrence_gates_few_kernel(const float* __restrict__ u, const float* __restrict
                             const float* __restrict__ wi, const float* __restrict__ bi, const float* __restrict__ lam, float gain,
                             float* __restrict__ a_out, float* __restrict__ drive_out, int n_tokens, int width, int bw) {
     extern __shared__ float us[];                   // [n_tokens][bw]
+    __shared__ float was[2][RG_FEW_OUTS][RG_K + 1];
+    __shared__ float wis[2][RG_FEW_OUTS][RG_K + 1];
     dd_launch_dependents();
-    const int b = blockIdx.y, j = threadIdx.x >> 5, o = blockIdx.x * RG_FEW_OUTS + (threadIdx.x & 31);
+    const int b = blockIdx.y, j = threadIdx.x >> 5, lane = threadIdx.x & 31, o0 = blockIdx.x * RG_FEW_OUTS, o = o0 + lane;
+    const int warps = blockDim.x >> 5;
     const bool live = o < bw;
-    const float* ra_row = wa + ((size_t)b * bw + (live ? o : 0)) * bw;
-    const float* ri_row = wi + ((size_t)b * bw + (live ? o : 0)) * bw;
+    const float* wa_b = wa + (size_t)b * bw * bw;
+    const float* wi_b = wi + (size_t)b * bw * bw;
     const float bias_a = live ? ba[b * bw + o] : 0.f, bias_i = live ? bi[b * bw + o] : 0.f;
     const float sp = live ? rg_softplus(lam[b * bw + o]) : 0.f;
+    auto stage = [&](int buf, int k0) {             // the weights do not depend on the kernel before
+        for (int r = j; r < RG_FEW_OUTS; r += warps) {
+            const bool in = o0 + r < bw && k0 + lane < bw;
+            was[buf][r][lane] = in ? wa_b[(size_t)(o0 + r) * bw + k0 + lane] : 0.f;
+            wis[buf][r][lane] = in ? wi_b[(size_t)(o0 + r) * bw + k0 + lane] : 0.f;
+        }
+    };
+    stage(0, 0);
     dd_grid_wait();
     for (int i = threadIdx.x; i < n_tokens * bw; i += blockDim.x) us[i] = u[(size_t)(i / bw) * width + b * bw + i % bw];
-    __syncthreads();
-    if (!live) return;
     const float* mine = us + j * bw;
     float ra = 0.f, ri = 0.f;
-    const bool wide = (bw & 3) == 0;
-    for (int k = 0; k < bw; k += 4) {
-        float a4[4], i4[4];
-        if (wide) {
-            const float4 x = *reinterpret_cast<const float4*>(ra_row + k), z = *reinterpret_cast<const float4*>(ri_row + k);
-            a4[0] = x.x; a4[1] = x.y; a4[2] = x.z; a4[3] = x.w; i4[0] = z.x; i4[1] = z.y; i4[2] = z.z; i4[3] = z.w;
-        } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) { a4[q] = k + q < bw ? ra_row[k + q] : 0.f; i4[q] = k + q < bw ? ri_row[k + q] : 0.f; }
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            if (k + q < bw) {
-                ra = fmaf(a4[q], mine[k + q], ra);
-                ri = fmaf(i4[q], mine[k + q], ri);
-            }
+    int buf = 0;
+    for (int k0 = 0; k0 < bw; k0 += RG_K, buf ^= 1) {
+        __syncthreads();                            // this stretch is staged; the other buffer has been read
+        if (k0 + RG_K < bw) stage(buf ^ 1, k0 + RG_K);
+        const int n = min(RG_K, bw - k0);
+        for (int kk = 0; kk < n; ++kk) {
+            ra = fmaf(was[buf][lane][kk], mine[k0 + kk], ra);
+            ri = fmaf(wis[buf][lane][kk], mine[k0 + kk], ri);
         }
     }
+    if (!live) return;
     const size_t at = (size_t)j * width + b * bw + o;
     const float r = rg_sigmoid(ra + bias_a), i = rg_sigmoid(ri + bias_i);
     const float log_a = -gain * r * sp;

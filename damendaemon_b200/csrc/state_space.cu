@@ -107,31 +107,47 @@ state_space_scan_kernel(const float* __restrict__ xbc, int xbc_stride, const T* 
             if (i < SS_TOKENS * ROW) staged[i] = ahead[j];
         }
         if (threadIdx.x < SS_TOKENS) {
-            const float dt = ss_softplus(dt_ahead + bias);
+            // tokens past the entry's end get a step of zero and no decay: they leave the state as it is, bit for bit
+            const bool real = t0 + (int)threadIdx.x < end;
+            const float dt = real ? ss_softplus(dt_ahead + bias) : 0.f;
             steps[threadIdx.x] = dt;
-            fades[threadIdx.x] = -expm1f(rate * dt);      // 1 - decay: a decay near one would lose its distance from one to rounding
+            fades[threadIdx.x] = real ? -expm1f(rate * dt) : 0.f;      // 1 - decay: a decay near one would lose its distance from one to rounding
         }
         __syncthreads();
         if (t0 + SS_TOKENS < end) fetch(t0 + SS_TOKENS);
         const int n = min(SS_TOKENS, end - t0);
-        for (int k = 0; k < n; ++k) {
-            const float* row = staged + k * ROW;
-            const float dt = steps[k], fade = fades[k];
-            const float x = row[2 * NP + my_col];
-            const float dtx = dt * x;
-            const float4 b0 = *reinterpret_cast<const float4*>(row + sub * 8), b1 = *reinterpret_cast<const float4*>(row + sub * 8 + 4);
-            const float4 c0 = *reinterpret_cast<const float4*>(row + NP + sub * 8), c1 = *reinterpret_cast<const float4*>(row + NP + sub * 8 + 4);
-            const float bn[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            const float cn[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            float y = 0.f;
+        // four tokens at a time: the state's chain runs through them one after the other (two multiply-adds a token and
+        // row), their read-outs and the exchanges between a column's lanes side by side
+        for (int k0 = 0; k0 < n; k0 += 4) {
+            float y[4], xs[4];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                s[r] = fmaf(dtx, bn[r], fmaf(-fade, s[r], s[r]));
-                y = fmaf(s[r], cn[r], y);
+            for (int i = 0; i < 4; ++i) {
+                const float* row = staged + (k0 + i) * ROW;
+                const float dt = steps[k0 + i], fade = fades[k0 + i];
+                xs[i] = row[2 * NP + my_col];
+                const float dtx = dt * xs[i];
+                const float4 b0 = *reinterpret_cast<const float4*>(row + sub * 8), b1 = *reinterpret_cast<const float4*>(row + sub * 8 + 4);
+                const float4 c0 = *reinterpret_cast<const float4*>(row + NP + sub * 8), c1 = *reinterpret_cast<const float4*>(row + NP + sub * 8 + 4);
+                const float bn[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                const float cn[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                float acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    s[r] = fmaf(dtx, bn[r], fmaf(-fade, s[r], s[r]));
+                    acc = fmaf(s[r], cn[r], acc);
+                }
+                y[i] = acc;
             }
 #pragma unroll
-            for (int o = LPC / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (live && sub == 0) out[(size_t)(t0 + k) * inner + h * dv + col] = fmaf(d_skip, x, y);
+            for (int o = LPC / 2; o > 0; o >>= 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) y[i] += __shfl_xor_sync(0xffffffffu, y[i], o);
+            }
+            if (live && sub == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (k0 + i < n) out[(size_t)(t0 + k0 + i) * inner + h * dv + col] = fmaf(d_skip, xs[i], y[i]);
+            }
         }
     }
     if (live) {
