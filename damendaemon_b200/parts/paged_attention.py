@@ -127,7 +127,8 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         kernels.kv_store(k[n1:], v[n1:], ctx.token_entry[n1:], ctx.positions[n1:], table, kv)
     if tcgen05:
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
-                                         out=out, kernel="tcgen05", k_new=k_new, v_new=v_new, store_new=fused_store, sink=sink, **masked)
+                                         out=out, kernel="tcgen05", k_new=k_new, v_new=v_new, store_new=fused_store,
+                                         **({} if sink is None else {"sink": sink}), **masked)
     if mma:
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
                                          out=out, **masked, **exact)

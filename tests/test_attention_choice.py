@@ -34,13 +34,15 @@ class Recorder:
         return 4
 
     def attention_decode(self, q, kv, token_entry, positions, table, n_heads, scale, window, n_splits=1, out=None,
-                         k_new=None, v_new=None, kernel="rows", chunk=None, gate=None):
-        self.calls.append(("decode-" + kernel, q.shape[0], token_entry is None, k_new is not None))
+                         k_new=None, v_new=None, kernel="rows", chunk=None, gate=None, keep_first=0, softcap=None, sink=None,
+                         exact_weights=False):
+        self.calls.append(("decode-" + kernel + ("+sink" if sink is not None else ""), q.shape[0], token_entry is None, k_new is not None))
         return out if out is not None else q
 
     def attention_prefill(self, q, kv, entry_start, entry_pos0, table, n_heads, scale, window=None, out=None, kernel="mma",
-                          k_new=None, v_new=None, store_new=False, chunk=None, gate=None):
-        self.calls.append(("prefill-" + kernel, entry_pos0.numel(), bool(store_new), table.shape[0]))
+                          k_new=None, v_new=None, store_new=False, chunk=None, gate=None, keep_first=0, softcap=None, sink=None,
+                          exact_weights=False):
+        self.calls.append(("prefill-" + kernel + ("+sink" if sink is not None else ""), entry_pos0.numel(), bool(store_new), table.shape[0]))
         return out if out is not None else q
 
     def attention_rows(self, q, kv, token_entry, positions, table, n_heads, scale, window=None, n_splits=1, out=None,
@@ -126,3 +128,20 @@ def test_no_tensor_core_prompt_kernel_means_the_general_kernel(monkeypatch):
     ctx, q, k, v, cache = step(2, [40])
     pa.paged_attention(ctx, q, k, v, cache, 25, 0.125)
     assert r.calls == [("kv_store", 42), ("rows", 42, 1)]
+
+
+def test_a_sink_alone_still_takes_the_tcgen05_prompt_kernel(recorder):
+    """One more term in the softmax's denominator and nothing else: portions go to the tcgen05 prompt kernel (which may write
+    the cache), single tokens to the row decode kernel; with capped scores as well, the mma.sync prompt kernel serves."""
+    sink = torch.zeros(25)
+    ctx, q, k, v, cache = step(3, [128, 256], aligned=True)
+    pa.paged_attention(ctx, q, k, v, cache, 25, 0.125, window=100, sink=sink)
+    assert recorder.calls == [("decode-rows+sink", 3, True, True), ("prefill-tcgen05+sink", 2, True, 2)]
+    recorder.calls.clear()
+    ctx, q, k, v, cache = step(0, [100])
+    pa.paged_attention(ctx, q, k, v, cache, 25, 0.125, window=100, sink=sink, softcap=30.0)
+    assert recorder.calls == [("kv_store", 100), ("prefill-mma+sink", 1, False, 1)]
+    recorder.calls.clear()
+    ctx, q, k, v, cache = step(8, [])
+    pa.paged_attention(ctx, q, k, v, cache, 25, 0.125, window=100, sink=sink)
+    assert recorder.calls == [("decode-rows+sink", 8, True, True)]          # the page-streaming kernel takes no sink
