@@ -437,7 +437,7 @@ def tetitar_configs(size, layers, vocab=50257):
     z = DESIGN_SIZES[size]
     out = {k: v for k, v in zokanex_configs(size, layers, vocab).items() if k in ("zokanex_attention_dense", "zokanex_retention_dense")}
     heads, width = z["heads"], z["width"]
-    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}
+    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
     attention = {"heads": heads, "kv_heads": heads, "dim": 64, "vdim": 64, "scale": 0.125, "rot": rot}
     left = {"heads": heads, "kv_heads": heads, "dim": 64, "vdim": 64, "scale": 0.125, "rot": {"dims": 64, "base": 10000.0}, "mask": {"size": 1024}}
     right = {"heads": heads, "vdim": 64, "state": 64, "groups": 1, "conv": 4, "norm_groups": 1}
@@ -446,7 +446,7 @@ def tetitar_configs(size, layers, vocab=50257):
 
     def model(entries, loop=None):
         config = {"architecture": "Tetitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
-                  "embedding": {"bigram": {"buckets": 99991, "mul_prev": 31, "mul_cur": 17}},
+                  "embedding": {"bigram": {"buckets": 99991, "mul_prev": 1009, "mul_cur": 613}},
                   "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in entries]}
         if loop:
             config["loop"] = dict(zip(("start", "stop", "times"), loop))

@@ -425,7 +425,7 @@ def _row_ops_case(which, rows, dev):
     pos = torch.arange(rows, dtype=torch.int32, device=dev) % (rows // n) + 1
     last = torch.zeros(n, dtype=torch.int32, device=dev)
     out = torch.empty(rows, width, device=dev)
-    run = lambda i: K.embed_pairs(ids, pos, ent, start, slot, table, pairs, last, 31, 17, out=out)
+    run = lambda i: K.embed_pairs(ids, pos, ent, start, slot, table, pairs, last, 1009, 613, out=out)
     return run, {"bytes": rows * width * 8, "flops": 2 * rows * width}
 
 

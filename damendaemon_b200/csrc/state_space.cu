@@ -28,7 +28,7 @@ conv_channels_kernel(const T* __restrict__ in, int in_stride, const float* __res
     const int t = blockIdx.y;
     const int c = blockIdx.x * 128 + threadIdx.x;
     if (c >= C) return;
-    float w[8];
+    float w[16];
     for (int j = 0; j < taps; ++j) w[j] = taps_w[(size_t)c * taps + j];
     float acc = bias ? bias[c] : 0.f;
     dd_grid_wait();
@@ -273,7 +273,7 @@ DD_API int dd_conv_channels(const void* in, int in_stride, const float* taps_w, 
                             const int* tok_entry, const int* entry_start, const int* entry_slot, float* out, int out_stride,
                             int n_tokens, int channels, int act, int dtype, void* stream) {
     if (n_tokens <= 0 || channels <= 0) return 0;
-    if (taps < 1 || taps > 8) return dd_fail("dd_conv_channels: %d taps are not supported (1 to 8)", taps);
+    if (taps < 1 || taps > 16) return dd_fail("dd_conv_channels: %d taps are not supported (1 to 16)", taps);
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(dd_ceil_div(channels, 128), n_tokens);
     if (dtype == DD_F32)

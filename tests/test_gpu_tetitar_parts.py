@@ -92,7 +92,7 @@ def test_tanh_norm_and_small_row_operations():
         assert torch.allclose(got.cpu().double(), want, atol=1e-5)
         # the cap and the element-wise gate
         z = randn(5, width, seed=10, scale=20.0)
-        assert torch.allclose(kernels.tanh_cap(z.to(DEV).clone(), 15.0).cpu(), 15.0 * torch.tanh(z / 15.0), atol=1e-5)
+        assert torch.allclose(kernels.tanh_cap(z.to(DEV).clone(), 11.0).cpu(), 11.0 * torch.tanh(z / 11.0), atol=1e-5)
         buffer = randn(5, 2 * width, seed=11).to(DEV)
         o = randn(5, width, seed=12).to(DEV)
         want = o * torch.sigmoid(buffer[:, width:])
@@ -101,7 +101,7 @@ def test_tanh_norm_and_small_row_operations():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads, kv_heads, d, dims, scaling", [(4, 2, 16, 8, (4.0, 1.0, 4.0, 64)), (1, 1, 32, 32, None),
-                                                               (6, 2, 12, 2, (8.0, 0.5, 2.0, 32)), (4, 4, 64, 48, (4.0, 1.0, 4.0, 2048))])
+                                                               (6, 2, 12, 2, (8.0, 0.5, 2.0, 32)), (4, 4, 64, 48, (8.0, 1.0, 4.0, 512))])
 def test_norm_over_the_whole_projection_with_rotation(dtype, heads, kv_heads, d, dims, scaling):
     """q and k normed over all their heads at once and rotated in halves at positions up to 5,000, against the plain
     functions; the frequencies are the plain ones (stretched or not)."""
@@ -176,7 +176,7 @@ def plain_state_space_core(xbc, dt_raw, dt_bias, a_log, skip, H, G, N, dv):
     return y.reshape(T, inner)
 
 
-@pytest.mark.parametrize("H, G, N, dv", [(4, 2, 32, 32), (2, 1, 16, 8), (6, 3, 20, 10), (1, 1, 8, 12), (4, 4, 128, 32), (2, 1, 24, 64), (3, 3, 1, 5)])
+@pytest.mark.parametrize("H, G, N, dv", [(4, 2, 48, 16), (2, 1, 16, 8), (6, 3, 20, 10), (1, 1, 8, 12), (4, 4, 128, 32), (2, 1, 24, 64), (3, 3, 1, 5)])
 def test_state_space_scan_in_portions_with_shuffled_slots(H, G, N, dv):
     """Two requests in portions down to one token beside each other, in slots that are not in order, against the plain
     recurrence; a prompt cut anywhere gives the same bits as the prompt whole."""
@@ -247,7 +247,7 @@ def test_gated_group_norm():
             assert torch.allclose(got, want, atol=1e-5 if dtype == torch.float32 else 3e-2)
 
 
-@pytest.mark.parametrize("width, blocks", [(256, 4), (48, 3), (40, 1), (60, 5), (300, 2), (7, 7)])
+@pytest.mark.parametrize("width, blocks", [(192, 4), (48, 3), (40, 1), (60, 5), (300, 2), (7, 7)])
 def test_gated_linear_recurrence_in_portions(width, blocks):
     """Gates and scan against the plain recurrence (its branches given), two requests in portions with shuffled slots; cut
     anywhere the bits are those of the whole prompt."""
@@ -339,7 +339,7 @@ def _paged(seq_k, seq_v, page_size, order_seed):
     return cache, table.to(DEV), extra
 
 
-@pytest.mark.parametrize("dk, dv, window", [(16, 8, 20), (128, 80, 136), (64, 64, 33), (24, 24, None)])
+@pytest.mark.parametrize("dk, dv, window", [(16, 8, 20), (96, 40, 72), (64, 64, 33), (24, 24, None)])
 def test_a_marked_key_at_every_edge_of_the_window_with_the_unit_term(dk, dv, window):
     """One key's score stands out (its key and the queries are scaled along one direction): queries for which that key is the
     window's oldest key, the first one outside, the query's own place, a page border, and far away, in a prompt and alone,

@@ -66,8 +66,8 @@ TINY_B = model(97, 48, [layer(parallel(3, 3, 8, 16, rot(4, 30.0), 7, 1, 12, 8, 1
 # of 256; the loop runs once (only its vector is added); a state of 128 and one of 24 (no power of two), as many groups as
 # heads; a window of 100; a recurrence with parts of 128
 TINY_C = model(300, 256, [layer(rglru(256, 2, 4), 256),
-                          layer(attention(4, 4, 64, rot(64, 10000.0, (4.0, 1.0, 4.0, 2048))), 512),
-                          layer(parallel(4, 2, 64, 64, rot(32, 500000.0), 100, 4, 32, 128, 4, 3, 4), 256),
+                          layer(attention(4, 4, 64, rot(64, 10000.0, (8.0, 1.0, 4.0, 512))), 512),
+                          layer(parallel(4, 2, 64, 64, rot(16, 200000.0), 100, 4, 32, 128, 4, 3, 4), 256),
                           layer(parallel(2, 2, 64, 64, rot(64, 100.0), 33, 2, 64, 24, 1, 2, 1), None)], loop=(1, 3, 1), cap=30.0)
 # D: awkward sizes: a width of 100, a vocabulary of 131, all layers in the loop, twice; three query heads on one key/value
 # head with keys of 20 and values of 12, a window of 33; six state-space heads in three groups, values of 10, a state of 20,
