@@ -1,5 +1,5 @@
 """Tetitar through the engine against the plain implementation, in 32-bit and in bfloat16, under every way of cutting
-the work, at four small configurations that differ in every size and option (tests/tetitar_tools.py)."""
+the work, at five small configurations that differ in every size and option (tests/tetitar_tools.py)."""
 import pytest
 import torch
 
@@ -10,7 +10,7 @@ from tetitar_tools import CONFIGS, make_tensors, plain_tensors, random_requests
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [1, 5, 19, 20, 21, 41, 100, 130], "B": [2, 6, 7, 8, 15, 50, 64, 90], "C": [1, 99, 100, 101, 134, 260, 300, 201],
-           "D": [1, 32, 33, 34, 67, 150, 9, 99]}
+           "D": [1, 32, 33, 34, 67, 150, 9, 99], "E": [1, 49, 50, 51, 128, 129, 260, 77]}
 FLOAT32_TOL = 2e-4
 TOL = {}
 

@@ -76,7 +76,13 @@ TINY_D = model(131, 100, [layer(parallel(3, 1, 20, 12, rot(6, 50.0), 33, 6, 10, 
                           layer(rglru(60, 5, 3), None),
                           layer(attention(6, 2, 12, rot(12, 1000.0)), 30)], loop=(0, 3, 2), pairs=None)
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# E: grouped heads at the sizes the tensor-core prompt kernels take: four query heads of 64 on two key/value heads whose
+# values are the keys; four heads of 128 on one key/value head with a window of 50 and the unit term; only the first layer
+# is repeated; a pair table of 31 buckets with both multipliers one
+TINY_E = model(150, 128, [layer(attention(4, 2, 64, rot(32, 1000.0)), 128),
+                          layer(parallel(4, 1, 128, 128, rot(64, 300.0), 50, 2, 16, 32, 2, 2, 1), 64)], loop=(0, 1, 2), pairs=(31, 1, 1))
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_tensors(config, seed, sharpen=3.0, dtype=torch.float32):
